@@ -1,0 +1,480 @@
+#!/usr/bin/env python
+"""Benchmark of the synaptic-propagation hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the 1,000,000-neuron event-driven CSR step — 1e6 pre x 1e6 post neurons, 1000
+outgoing synapses per neuron (1e9 stored synapses: 4 GB int32 indices + 4 GB float32 weights
+U(0,1)), a fresh float32 spike vector per step with 1 % of the entries set (seeded numpy
+PCG64 draws, `brainpylib_b200/workloads.py`), `event_csr_matvec(..., transpose=True)`.
+One "step" = one call.  Metric: synaptic operations per second = (sum over the step's active
+rows of the row length) / time, whole job.
+
+Prints ONE JSON line (rank 0).  `value` is timed with the matrix, the spikes and the output
+resident in HBM (CUDA graph of the K steps, CUDA events, max over ranks); `e2e` goes through
+the public operator with host spike buffers in and host result buffers out every step;
+`roofline` is for the scatter kernel alone (CUDA events recorded around it by the library's
+profiling hook); `cpu_baseline` / `--impl reference` time the reference's own CPU kernel
+(lib/cpu_event_sum.cc compiled into oracle/_ref, else this repository's CPU restatement).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+N_NEURONS = 1_000_000
+DEGREE = 1000
+CPU_SAMPLE_ROWS = 100_000   # rows of the matrix the CPU legs work on (the first generation chunk)
+RATE = 0.01
+METRIC = 'synaptic_ops_per_sec'
+UNIT = 'SyOp/s'
+WORKLOAD = 'C3 event_csr_matvec transpose=True: 1e6 neurons x 1000 synapses (1e9 nnz, heter f32 U(0,1)), ' \
+           'f32 events 1% firing, fresh spikes every step'
+
+
+def log(*a):
+  print(*a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+  path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+  if os.path.exists(path):
+    try:
+      return float(json.load(open(path))['hbm_gbs']), 'measured (MEASURED_PEAKS.json hbm_gbs)'
+    except Exception:
+      pass
+  return 6650.0, 'fallback (6.65 TB/s, earlier measurement on this pool)'
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+  """Samples SM clock and throttle reasons through NVML while the GPU is busy."""
+
+  def __init__(self, index):
+    self.samples, self.reasons, self.max_mhz = [], set(), None
+    self._stop = threading.Event()
+    self._thread = None
+    try:
+      import pynvml
+      pynvml.nvmlInit()
+      self.nv = pynvml
+      self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+      self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+    except Exception as e:   # NVML missing: report nothing rather than fail the run
+      self.nv = None
+      log(f'[bench] NVML unavailable: {e}')
+
+  def _loop(self):
+    nv = self.nv
+    names = {
+      'hw_slowdown': getattr(nv, 'nvmlClocksThrottleReasonHwSlowdown', 0x8),
+      'hw_thermal_slowdown': getattr(nv, 'nvmlClocksThrottleReasonHwThermalSlowdown', 0x40),
+      'sw_thermal_slowdown': getattr(nv, 'nvmlClocksThrottleReasonSwThermalSlowdown', 0x20),
+      'sw_power_cap': getattr(nv, 'nvmlClocksThrottleReasonSwPowerCap', 0x4),
+    }
+    while not self._stop.is_set():
+      try:
+        util = nv.nvmlDeviceGetUtilizationRates(self.h).gpu
+        mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+        mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        self.samples.append((mhz, util))
+        for k, bit in names.items():
+          if mask & bit:
+            self.reasons.add(k)
+      except Exception:
+        pass
+      time.sleep(0.002)
+
+  def __enter__(self):
+    if self.nv is not None:
+      self._thread = threading.Thread(target=self._loop, daemon=True)
+      self._thread.start()
+    return self
+
+  def __exit__(self, *exc):
+    self._stop.set()
+    if self._thread is not None:
+      self._thread.join()
+
+  def summary(self):
+    if not self.samples:
+      return {'sm_mhz': None, 'sm_max_mhz': self.max_mhz, 'reasons': [], 'samples': 0}
+    busy = [m for m, u in self.samples if u > 0] or [m for m, _ in self.samples]
+    return {'sm_mhz': float(np.median(busy)), 'sm_max_mhz': self.max_mhz, 'reasons': sorted(self.reasons),
+            'samples': len(self.samples), 'samples_under_load': len(busy)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------------
+def build_workload(n_steps, keep_host_matrix, device=None, shard=None):
+  """The matrix on `device` (or only on the host) plus `n_steps` spike vectors (host, float32).
+
+  `shard` = (rank, world): keep only the synapses whose target lies in this rank's contiguous
+  range of post-synaptic neurons (own indptr), filtered on the GPU chunk by chunk.
+  """
+  from brainpylib_b200 import workloads
+  import torch
+  t0 = time.time()
+  host = {'indices': [], 'data': []}
+  dev = {'indices': [], 'data': []}
+  lengths = []
+  lo = hi = None
+  if shard is not None:
+    rank, world = shard
+    per = (N_NEURONS + world - 1) // world
+    lo, hi = rank * per, min(N_NEURONS, (rank + 1) * per)
+  masks = []
+  rng = None
+  for kind, c, arr in workloads.c3_matrix_chunks(N_NEURONS):
+    if kind == 'rng':
+      rng = arr
+      continue
+    if keep_host_matrix and c == 0:
+      host[kind].append(arr)     # the CPU legs run on the first 100,000 rows (chunk 0) only
+    if device is not None:
+      t = torch.from_numpy(arr).to(device, non_blocking=False)
+      if shard is not None:
+        if kind == 'indices':
+          m = (t >= lo) & (t < hi)
+          masks.append(m)
+          lengths.append(m.view(-1, DEGREE).sum(dim=1, dtype=torch.int32))
+          t = t[m] - lo
+        else:
+          t = t[masks[c]]
+          masks[c] = None
+      dev[kind].append(t)
+  events = [workloads.c3_events(rng, N_NEURONS, RATE) for _ in range(n_steps)]
+  out = {'events': events, 'gen_seconds': None}
+  if device is not None:
+    out['indices'] = torch.cat(dev['indices'])
+    dev['indices'] = None
+    out['data'] = torch.cat(dev['data'])
+    dev['data'] = None
+    if shard is None:
+      out['indptr'] = torch.arange(0, N_NEURONS * DEGREE + 1, DEGREE, dtype=torch.int32, device=device)
+      out['shape'] = (N_NEURONS, N_NEURONS)
+    else:
+      ptr = torch.zeros(N_NEURONS + 1, dtype=torch.int64, device=device)
+      ptr[1:] = torch.cumsum(torch.cat(lengths).to(torch.int64), 0)
+      out['indptr'] = ptr.to(torch.int32)
+      out['shape'] = (N_NEURONS, hi - lo)
+    torch.cuda.synchronize()
+  if keep_host_matrix:
+    out['host_indices'], out['host_data'] = host['indices'][0], host['data'][0]
+    out['host_indptr'] = np.arange(0, CPU_SAMPLE_ROWS * DEGREE + 1, DEGREE, dtype=np.int32)
+  out['gen_seconds'] = time.time() - t0
+  return out
+
+
+def cpu_reference_kernel():
+  """(callable(events_f32) -> y, kind): the reference's own compiled CPU kernel when oracle/_ref
+  holds it, else this repository's CPU restatement of it."""
+  from oracle import ref
+  if ref.available_cpu():
+    return 'reference'
+  return 'port'
+
+
+CPU_SAMPLE = ('pre-synaptic rows 0..99,999 of the same matrix (1e8 synapses, all 1e6 post-synaptic targets) with '
+              'the same spike vectors restricted to those rows: ~1e6 synaptic ops per step')
+
+
+def time_cpu_steps(work, n_steps, budget_seconds=None):
+  """Times the reference CPU path (serial C++: 1 core) on a bounded sample of the workload: the first
+  100,000 rows of the matrix, every step's spikes restricted to those rows."""
+  from oracle import cpu as oracle_cpu
+  from oracle import ref
+  kind = cpu_reference_kernel()
+  ops, t_total, done = 0, 0.0, 0
+  for s in range(n_steps):
+    ev = work['events'][s % len(work['events'])][:CPU_SAMPLE_ROWS]
+    if kind == 'reference':
+      evb = ev != 0    # lib/cpu_event_sum.cc takes bool events; same truthiness test as the GPU op
+      t0 = time.perf_counter()
+      ref.csr_event_sum(evb, work['host_indices'], work['host_indptr'], work['host_data'], N_NEURONS)
+      t_total += time.perf_counter() - t0
+    else:
+      t0 = time.perf_counter()
+      oracle_cpu.event_csr_matvec(work['host_data'], work['host_indices'], work['host_indptr'], ev,
+                                  shape=(CPU_SAMPLE_ROWS, N_NEURONS), transpose=True)
+      t_total += time.perf_counter() - t0
+    ops += int(np.count_nonzero(ev)) * DEGREE
+    done += 1
+    if budget_seconds is not None and t_total > budget_seconds:
+      break
+  return ops / t_total, kind, done, t_total
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+  rank = int(os.environ.get('RANK', '0'))
+  if rank != 0:
+    return
+  total = args.warmup + args.steps
+  work = build_workload(total, keep_host_matrix=True, device=None)
+  log(f'[bench] reference arm: host matrix built in {work["gen_seconds"]:.1f}s')
+  if args.warmup:
+    time_cpu_steps({**work, 'events': work['events'][:args.warmup]}, args.warmup)
+  value, kind, done, seconds = time_cpu_steps({**work, 'events': work['events'][args.warmup:]}, args.steps)
+  line = {
+    'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': done,
+    'warmup': args.warmup, 'ms_per_step': seconds / done * 1e3, 'higher_is_better': True, 'scaling': 'strong',
+    'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+    'config': {'workload': WORKLOAD, 'reference_code': 'lib/cpu_event_sum.cc cpu_csr_event_sum_heter_f32_i32 '
+               '(serial C++) on the host'},
+    'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': 1, 'kind': kind,
+                     'sample': f'{done} steps on {CPU_SAMPLE}', 'host_cores_available': os.cpu_count()},
+    'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    'gpu_launches': 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+  import torch
+  import torch.distributed as dist
+  import brainpylib_b200 as bpl
+  from brainpylib_b200 import _lib, event_ops, gpu_ops
+
+  world = int(os.environ.get('WORLD_SIZE', '1'))
+  rank = int(os.environ.get('RANK', '0'))
+  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+  if not torch.cuda.is_available():
+    raise SystemExit('bench.py needs a CUDA device (no CPU fallback)')
+  torch.cuda.set_device(local_rank)
+  device = torch.device('cuda', local_rank)
+  if world > 1:
+    dist.init_process_group('nccl', device_id=device)
+  _lib.lib()   # fail loudly if the CUDA library is missing
+
+  K, W = args.steps, args.warmup
+  total = W + K
+  want_cpu = (world == 1 and rank == 0 and not args.no_cpu_baseline)
+  work = build_workload(total, keep_host_matrix=want_cpu, device=device, shard=(rank, world) if world > 1 else None)
+  log(f'[bench] rank {rank}: workload built in {work["gen_seconds"]:.1f}s, '
+      f'{work["indices"].numel():,} synapses on device')
+  shape = work['shape']
+  ops_per_step = [int(np.count_nonzero(e)) * DEGREE for e in work['events']]
+  ev_host = torch.from_numpy(np.stack(work['events'])).pin_memory()
+  ev_dev = ev_host.to(device)
+  y = torch.empty(shape[1], dtype=torch.float32, device=device)
+  name = 'event_csr_matvec_heter_float_float'
+  opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
+  ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
+
+  # N > 1: every rank produces the spikes of its own 1/N of the neurons and the dense spike vector is
+  # all-gathered (NCCL over NVLink) inside the step; the matrix shard then needs no further exchange.
+  per = N_NEURONS // world
+  ev_full = torch.empty(N_NEURONS, dtype=torch.float32, device=device) if world > 1 else None
+
+  def step(s, out=y):
+    events = ev_dev[s]
+    if world > 1:
+      dist.all_gather_into_tensor(ev_full, ev_dev[s, rank * per:(rank + 1) * per])
+      events = ev_full
+    event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], events, shape=shape,
+                                   transpose=True, out=out, workspace=ws)
+
+  # sanity: one step against a plain torch scatter on the same device
+  step(0)
+  rows = torch.nonzero(ev_dev[0]).flatten()
+  starts = work['indptr'][rows].to(torch.int64)
+  lens = (work['indptr'][rows + 1] - work['indptr'][rows]).to(torch.int64)
+  pos = torch.repeat_interleave(starts - torch.cumsum(lens, 0) + lens, lens) + torch.arange(int(lens.sum()),
+                                                                                            device=device)
+  chk = torch.zeros_like(y).index_add_(0, work['indices'][pos].to(torch.int64), work['data'][pos])
+  err = (chk - y).abs().max().item()
+  if not err < 1e-5 * 1000:
+    raise SystemExit(f'bench sanity check failed: max abs error {err}')
+  del rows, starts, lens, pos, chk
+
+  sampler = ClockSampler(local_rank)
+  with sampler:
+    # ---- value: K steps captured in one CUDA graph, inputs resident in HBM ----
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+      for s in range(min(W, 3)):
+        step(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+      for s in range(W, W + K):
+        step(s)
+    warm = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(warm, stream=side):
+      for s in range(W):
+        step(s)
+    if W:
+      warm.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+      dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+      t = torch.tensor([ms], device=device)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      ms = t.item()
+    total_ops = sum(ops_per_step[W:W + K])
+    value = total_ops / (ms * 1e-3)
+
+    # ---- roofline: the scatter kernel alone, timed by events recorded around it ----
+    lib = _lib.lib()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for s in range(K):
+      a, b = pairs[s]
+      a.record()   # creates the underlying CUDA events
+      b.record()
+    torch.cuda.synchronize()
+    import ctypes
+    for s in range(K):
+      a, b = pairs[s]
+      lib.bpl_profile_scatter_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
+      step(W + s)
+    lib.bpl_profile_scatter_events(None, None)
+    torch.cuda.synchronize()
+    k_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
+
+    # ---- e2e: public operator, host spikes in, host result out, every step ----
+    e2e = run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step)
+    if world > 1:
+      t = torch.tensor([e2e['ms']], device=device)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      e2e['ms'] = t.item()
+    e2e_value = total_ops / (e2e['ms'] * 1e-3)
+
+  peak, peak_src = measured_peaks()
+  n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
+  s_local = float(work['indices'].numel()) / (N_NEURONS * DEGREE) * n_act * DEGREE   # this rank's synapses per step
+  # algorithmic bytes of one scatter launch: indices + weights of the active rows (8 B per synapse),
+  # their indptr pairs (8 B per active row) and the write-back of y (4 B per output neuron)
+  k_bytes = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
+  # whole step: + the spike scan (4 B per pre neuron) and the zero-fill of y (4 B per output neuron)
+  step_bytes = k_bytes + 4.0 * N_NEURONS + 4.0 * shape[1]
+  achieved = k_bytes / (k_ms * 1e-3) / 1e9
+  roofline = {
+    'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec>', 'achieved': achieved, 'peak': peak,
+    'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
+    'traffic': None, 'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
+    'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
+             'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak},
+  }
+
+  line = {
+    'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': K, 'warmup': W,
+    'ms_per_step': ms / K, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
+    'data': 'synthetic',
+    'config': {'workload': WORKLOAD, 'l2': 'inputs larger than L2: each step streams a different ~80 MB of the '
+               '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
+               'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
+               'ranks; each rank owns 1/N of the spike sources; NCCL all-gather of the dense spike vector '
+               'inside every step'},
+    'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
+            'ms_per_step': e2e['ms'] / K},
+    'gpu_launches': 2 * K,
+    'roofline': roofline,
+    'clocks': sampler.summary(),
+  }
+
+  if want_cpu:
+    cpu_value, kind, done, seconds = time_cpu_steps(work, 100000, budget_seconds=10.0)
+    line['cpu_baseline'] = {'value': cpu_value, 'unit': UNIT, 'cores': 1, 'kind': kind,
+                            'sample': f'{done} steps ({seconds:.1f} s of CPU time) on {CPU_SAMPLE}; '
+                                      'lib/cpu_event_sum.cc serial C++',
+                            'host_cores_available': os.cpu_count()}
+  if rank == 0:
+    print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
+  """Three streams (copy in, compute, copy out) with double buffers: step s+1's spikes are copied in
+  while step s computes and step s-1's result is copied out."""
+  s_in, s_c, s_out = (torch.cuda.Stream(device) for _ in range(3))
+  n_buf = 3
+  ev_buf = [torch.empty(shape[0], dtype=torch.float32, device=device) for _ in range(n_buf)]
+  y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+  done_in = [None] * n_buf
+  done_c = [None] * n_buf
+  done_out = [None] * n_buf
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+  def run(first, count, timed):
+    torch.cuda.synchronize()
+    if timed:
+      with torch.cuda.stream(s_in):
+        e0.record()
+    for i in range(count):
+      s, b = first + i, i % n_buf
+      with torch.cuda.stream(s_in):
+        if done_c[b] is not None:
+          s_in.wait_event(done_c[b])       # the buffer's previous reader has finished
+        ev_buf[b].copy_(ev_host[s], non_blocking=True)
+        done_in[b] = torch.cuda.Event()
+        done_in[b].record()
+      with torch.cuda.stream(s_c):
+        s_c.wait_event(done_in[b])
+        yb = bpl.event_csr_matvec(work['data'], work['indices'], work['indptr'], ev_buf[b], shape=shape,
+                                  transpose=True)
+        done_c[b] = torch.cuda.Event()
+        done_c[b].record()
+      with torch.cuda.stream(s_out):
+        s_out.wait_event(done_c[b])
+        y_host[b].copy_(yb, non_blocking=True)
+        yb.record_stream(s_out)
+        done_out[b] = torch.cuda.Event()
+        done_out[b].record()
+    if timed:
+      with torch.cuda.stream(s_out):
+        s_out.wait_stream(s_c)
+        e1.record()
+    torch.cuda.synchronize()
+
+  run(0, max(W, 1), False)
+  run(W, K, True)
+  return {'ms': e0.elapsed_time(e1), 'h2d': 4 * shape[0], 'd2h': 4 * shape[1]}
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument('--gpus', type=int, default=1)
+  ap.add_argument('--steps', type=int, default=200)
+  ap.add_argument('--warmup', type=int, default=5)
+  ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+  ap.add_argument('--no-cpu-baseline', action='store_true')
+  args = ap.parse_args()
+  if args.warmup < 3 and args.impl == 'ours':
+    log('[bench] note: fewer than 3 warm-up steps requested; the timing rules ask for >= 3')
+  if args.impl == 'reference':
+    run_reference(args)
+  else:
+    run_ours(args)
+
+
+if __name__ == '__main__':
+  main()

@@ -1,0 +1,514 @@
+// Stored-matrix (CSR) synaptic propagation for sm_100a:
+//   event_csr_matvec  (replaces lib/gpu_event_csr_matvec.cu of the reference)
+//   csr_matvec        (replaces lib/gpu_csr_matvec.cu) and its transposed form
+//   gpu_csr_event_sum (replaces the CSR half of lib/gpu_event_sum.cu)
+//
+// Scatter direction (y = A^T x, "transpose"): the spike vector is first compacted into a
+// list of active rows (scan_events_kernel, which also zero-fills y), then only those rows
+// are streamed with 128-bit loads and scattered with one `red.global.add` per synapse
+// (row_scatter_kernel).  Homogeneous weights use the same float reductions: k additions
+// of one value give the same float in any order, so the result equals the reference's
+// sequential sum bit for bit.
+//
+// Gather direction (y = A x): a sub-warp per row streams the whole matrix with 128-bit
+// loads and reduces with shuffles (row_gather_kernel).
+#include "abi.h"
+#include "common.cuh"
+
+namespace bpl {
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// Spike compaction
+// ------------------------------------------------------------------------------------------
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_WARP_SPAN = 512;                                   // events per warp per tile
+constexpr int SCAN_TILE = (SCAN_THREADS / 32) * SCAN_WARP_SPAN;       // 4096 events per block per tile
+constexpr int MAX_CHUNKS = 1024;                                      // chunk = what one block compacts
+
+struct ScanPlan {
+    uint32_t chunk;     // events per chunk, a multiple of SCAN_TILE
+    uint32_t n_chunks;  // <= MAX_CHUNKS
+};
+
+inline ScanPlan plan_scan(uint32_t n_row) {
+    const uint64_t tiles = (static_cast<uint64_t>(n_row) + SCAN_TILE - 1) / SCAN_TILE;
+    const uint64_t tiles_per_chunk = tiles == 0 ? 1 : (tiles + MAX_CHUNKS - 1) / MAX_CHUNKS;
+    ScanPlan p;
+    p.chunk = static_cast<uint32_t>(tiles_per_chunk * SCAN_TILE);
+    p.n_chunks = static_cast<uint32_t>((static_cast<uint64_t>(n_row) + p.chunk - 1) / p.chunk);
+    return p;
+}
+
+// Workspace of the transposed event product: counts[MAX_CHUNKS] then ids[n_row] (uint32).
+// Chunk c owns ids[c * chunk, (c + 1) * chunk): its active rows, ascending, counts[c] of them.
+// Nothing in it needs initialising and no atomics are used, so the list is a fixed function
+// of the events (ascending row order).
+inline size_t scatter_workspace_bytes(uint32_t n_row) {
+    return (static_cast<size_t>(MAX_CHUNKS) + n_row) * sizeof(uint32_t);
+}
+
+template<typename T, typename E>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_events_kernel(const E *__restrict__ events, const uint32_t n_row, const uint32_t chunk,
+                   const uint32_t n_chunks, T *__restrict__ y, const uint32_t n_out,
+                   uint32_t *__restrict__ counts, uint32_t *__restrict__ ids) {
+    // (1) zero-fill the output (the reference does it with a cudaMemset on the wrong stream,
+    //     lib/gpu_event_csr_matvec.cu:170).
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * SCAN_THREADS + threadIdx.x; i < n_out;
+         i += static_cast<uint64_t>(gridDim.x) * SCAN_THREADS)
+        y[i] = T(0);
+
+    if (blockIdx.x >= n_chunks) return;
+
+    // (2) compact this block's chunk.  A warp reads 512 consecutive events as 16 coalesced
+    //     loads; each ballot is one word of the natural-order bitmap.
+    __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t chunk_begin = static_cast<uint64_t>(blockIdx.x) * chunk;
+    const uint64_t chunk_end = min(chunk_begin + chunk, static_cast<uint64_t>(n_row));
+    uint32_t *out = ids + chunk_begin;
+    uint32_t running = 0;
+
+    for (uint64_t tile = chunk_begin; tile < chunk_end; tile += SCAN_TILE) {
+        const uint64_t base = tile + static_cast<uint64_t>(warp) * SCAN_WARP_SPAN;
+        bool act[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const uint64_t i = base + k * 32 + lane;
+            act[k] = (i < chunk_end) && is_event(events[i]);
+        }
+        uint32_t bits[16];
+        uint32_t total = 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            bits[k] = __ballot_sync(FULL_MASK, act[k]);
+            total += __popc(bits[k]);
+        }
+        if (lane == 0) warp_total[warp] = total;
+        __syncthreads();
+        uint32_t offset = running, tile_total = 0;
+#pragma unroll
+        for (int w = 0; w < SCAN_THREADS / 32; ++w) {
+            const uint32_t t = warp_total[w];
+            if (w < static_cast<int>(warp)) offset += t;
+            tile_total += t;
+        }
+        __syncthreads();
+        const uint32_t below = (1u << lane) - 1u;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            if (act[k]) out[offset + __popc(bits[k] & below)] = static_cast<uint32_t>(base + k * 32 + lane);
+            offset += __popc(bits[k]);
+        }
+        running += tile_total;
+    }
+    if (threadIdx.x == 0) counts[blockIdx.x] = running;
+}
+
+// ------------------------------------------------------------------------------------------
+// Row streaming helpers: 4 consecutive matrix entries at a 16-byte aligned position
+// ------------------------------------------------------------------------------------------
+template<typename T>
+struct Quad { T v[4]; };
+
+__device__ __forceinline__ void load_quad(const float *p, Quad<float> &q) {
+    const uint4 u = ldg_stream_u4(p);
+    q.v[0] = __uint_as_float(u.x); q.v[1] = __uint_as_float(u.y);
+    q.v[2] = __uint_as_float(u.z); q.v[3] = __uint_as_float(u.w);
+}
+__device__ __forceinline__ void load_quad(const double *p, Quad<double> &q) {
+    const uint4 a = ldg_stream_u4(p), b = ldg_stream_u4(p + 2);
+    q.v[0] = __hiloint2double(a.y, a.x); q.v[1] = __hiloint2double(a.w, a.z);
+    q.v[2] = __hiloint2double(b.y, b.x); q.v[3] = __hiloint2double(b.w, b.z);
+}
+
+constexpr int ROW_THREADS = 256;
+constexpr int ROW_WARPS = ROW_THREADS / 32;
+
+// How many pieces a row is cut into so that work items stay near 256 entries: keeps the
+// last wave of a persistent grid short.  Uniform over the grid (a function of the mean row length).
+__device__ __forceinline__ uint32_t pieces_per_row(uint32_t nse, uint32_t n_row) {
+    const uint32_t mean = n_row ? nse / n_row : 0;
+    const uint32_t s = mean / 320u;
+    return s < 1u ? 1u : (s > 16u ? 16u : s);
+}
+
+// Boundary h (0..S) of row [start, end) cut into S pieces; interior cuts fall on multiples of 4
+// entries so that every piece starts on a 16-byte boundary of the index and weight arrays.
+__device__ __forceinline__ uint32_t piece_cut(uint32_t start, uint32_t end, uint32_t h, uint32_t S) {
+    if (h == 0) return start;
+    if (h >= S) return end;
+    const uint64_t c = start + static_cast<uint64_t>(end - start) * h / S;
+    const uint64_t r = (c + 3u) & ~static_cast<uint64_t>(3u);
+    return static_cast<uint32_t>(r < end ? r : end);
+}
+
+// One warp scatters entries [a, b) of the matrix: y[indices[e]] += weight(e) * scale.
+template<typename T, bool HOMO, bool SCALED, bool VEC>
+__device__ __forceinline__ void scatter_span(const uint32_t *__restrict__ indices, const T *__restrict__ data,
+                                             const T homo_w, const T scale, const uint32_t a, const uint32_t b,
+                                             const uint32_t nse, T *__restrict__ y, const uint32_t lane) {
+    if (VEC) {
+        const uint32_t g_begin = a >> 2, g_end = (b + 3u) >> 2;   // 4-entry groups touched
+        const uint32_t g_full = nse >> 2;                         // groups lying wholly inside the arrays
+        for (uint32_t g0 = g_begin; g0 < g_end; g0 += 128u) {
+            uint4 ix[4];
+            Quad<T> wq[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t g = g0 + lane + 32u * u;
+                if (g < g_end && g < g_full) {
+                    ix[u] = ldg_stream_u4(indices + 4ull * g);
+                    if (!HOMO) load_quad(data + 4ull * g, wq[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t g = g0 + lane + 32u * u;
+                if (g >= g_end) continue;
+                if (g < g_full) {
+                    const uint32_t c[4] = {ix[u].x, ix[u].y, ix[u].z, ix[u].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t pos = 4u * g + e;
+                        if (pos >= a && pos < b) {
+                            T w = HOMO ? homo_w : wq[u].v[e];
+                            if (SCALED) w = w * scale;
+                            atomicAdd(y + c[e], w);
+                        }
+                    }
+                } else {  // ragged tail of the arrays: element-wise
+                    for (uint32_t pos = max(4u * g, a); pos < b; ++pos) {
+                        T w = HOMO ? homo_w : data[pos];
+                        if (SCALED) w = w * scale;
+                        atomicAdd(y + indices[pos], w);
+                    }
+                }
+            }
+        }
+    } else {
+        for (uint32_t pos = a + lane; pos < b; pos += 32u) {
+            T w = HOMO ? homo_w : data[pos];
+            if (SCALED) w = w * scale;
+            atomicAdd(y + indices[pos], w);
+        }
+    }
+}
+
+// Scatter product over a list of rows.
+//   LIST = true : rows come from the compacted spike list (event-driven, scale = 1).
+//   LIST = false: every row, scaled by x[row]  (y = A^T x for a dense x).
+template<typename T, bool HOMO, bool LIST, bool VEC>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_scatter_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restrict__ indptr,
+                   const T *__restrict__ data, const T *__restrict__ x, const uint32_t n_row,
+                   const uint32_t chunk, const uint32_t n_chunks, const uint32_t *__restrict__ counts,
+                   const uint32_t *__restrict__ ids, T *__restrict__ y) {
+    __shared__ uint32_t prefix[MAX_CHUNKS + 1];
+    __shared__ uint32_t warp_total[ROW_WARPS];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t n_list = n_row;
+
+    if (LIST) {  // exclusive prefix over the chunk counts: 4 counts per thread, 256 threads
+        uint32_t c[4];
+        uint32_t s = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t k = threadIdx.x * 4 + j;
+            c[j] = k < n_chunks ? counts[k] : 0u;
+            s += c[j];
+        }
+        uint32_t incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(FULL_MASK, incl, o);
+            if (lane >= static_cast<uint32_t>(o)) incl += t;
+        }
+        if (lane == 31) warp_total[warp] = incl;
+        __syncthreads();
+        uint32_t base = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < ROW_WARPS; ++w) {
+            const uint32_t t = warp_total[w];
+            if (w < static_cast<int>(warp)) base += t;
+            total += t;
+        }
+        uint32_t run = base + incl - s;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            prefix[threadIdx.x * 4 + j] = run;
+            run += c[j];
+        }
+        if (threadIdx.x == 0) prefix[MAX_CHUNKS] = total;
+        __syncthreads();
+        n_list = total;
+    }
+    if (n_list == 0) return;
+
+    const uint32_t nse = indptr[n_row];
+    const uint32_t S = pieces_per_row(nse, n_row);
+    const T homo_w = HOMO ? data[0] : T(0);
+    const uint64_t n_items = static_cast<uint64_t>(n_list) * S;
+    const uint64_t n_warps = static_cast<uint64_t>(gridDim.x) * ROW_WARPS;
+
+    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * ROW_WARPS + warp; item < n_items; item += n_warps) {
+        const uint32_t li = static_cast<uint32_t>(item / S), h = static_cast<uint32_t>(item % S);
+        uint32_t row = li;
+        if (LIST) {  // chunk c with prefix[c] <= li < prefix[c + 1]
+            uint32_t lo = 0, hi = n_chunks;
+            while (hi - lo > 1) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (prefix[mid] <= li) lo = mid; else hi = mid;
+            }
+            row = ids[static_cast<uint64_t>(lo) * chunk + (li - prefix[lo])];
+        }
+        T scale = T(1);
+        if (!LIST) scale = x[row];
+        const uint32_t start = indptr[row], end = indptr[row + 1];
+        const uint32_t a = piece_cut(start, end, h, S), b = piece_cut(start, end, h + 1, S);
+        if (a < b) scatter_span<T, HOMO, !LIST, VEC>(indices, data, homo_w, scale, a, b, nse, y, lane);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Gather direction: y[r] = sum_j w_j * f(x[col_j]) with a group of `lpr` lanes per row
+// ------------------------------------------------------------------------------------------
+// EVENT = true : f = truthiness of the event; homogeneous weights count hits and scale once
+//                (equal to the reference CPU kernel's float64 accumulation,
+//                brainpylib/_src/event_ops/event_csr_matvec.py:334-357).
+// EVENT = false: f = x, products accumulated with fused multiply-adds as the reference
+//                `sum += data[e] * x[col]` compiles to (lib/gpu_csr_matvec.cu:163).
+template<typename T, typename X, bool HOMO, bool EVENT, bool VEC>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restrict__ indptr,
+                  const T *__restrict__ data, const X *__restrict__ x, const uint32_t n_row,
+                  T *__restrict__ y) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t nse = indptr[n_row];
+    const uint32_t mean = n_row ? nse / n_row : 0;
+    // lanes per row: each lane takes 4 entries per step
+    const uint32_t lpr = mean <= 16u ? 4u : (mean <= 32u ? 8u : (mean <= 64u ? 16u : 32u));
+    const uint32_t rows_per_warp = 32u / lpr;
+    const uint32_t sub = lane / lpr, sl = lane % lpr;
+    const T homo_w = HOMO ? data[0] : T(0);
+    const uint64_t n_warps = static_cast<uint64_t>(gridDim.x) * ROW_WARPS;
+    const uint64_t n_groups = (static_cast<uint64_t>(n_row) + rows_per_warp - 1) / rows_per_warp;
+    const uint32_t g_full = nse >> 2;
+
+    for (uint64_t wg = static_cast<uint64_t>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); wg < n_groups;
+         wg += n_warps) {
+        const uint64_t row64 = wg * rows_per_warp + sub;
+        const bool live = row64 < n_row;
+        const uint32_t row = live ? static_cast<uint32_t>(row64) : 0u;
+        const uint32_t start = live ? indptr[row] : 0u, end = live ? indptr[row + 1] : 0u;
+        T acc = T(0);
+        uint32_t hits = 0;
+        if (VEC) {
+            const uint32_t g_begin = start >> 2, g_end = (end + 3u) >> 2;
+            for (uint32_t g = g_begin + sl; g < g_end; g += lpr) {
+                if (g < g_full) {
+                    const uint4 ix = ldg_stream_u4(indices + 4ull * g);
+                    Quad<T> wq;
+                    if (!HOMO) load_quad(data + 4ull * g, wq);
+                    const uint32_t c[4] = {ix.x, ix.y, ix.z, ix.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t pos = 4u * g + e;
+                        if (pos >= start && pos < end) {
+                            if (EVENT) {
+                                if (is_event(x[c[e]])) { if (HOMO) ++hits; else acc += wq.v[e]; }
+                            } else {
+                                acc += (HOMO ? homo_w : wq.v[e]) * static_cast<T>(x[c[e]]);
+                            }
+                        }
+                    }
+                } else {
+                    for (uint32_t pos = max(4u * g, start); pos < end; ++pos) {
+                        const uint32_t col = indices[pos];
+                        if (EVENT) {
+                            if (is_event(x[col])) { if (HOMO) ++hits; else acc += data[pos]; }
+                        } else {
+                            acc += (HOMO ? homo_w : data[pos]) * static_cast<T>(x[col]);
+                        }
+                    }
+                }
+            }
+        } else {
+            for (uint32_t pos = start + sl; pos < end; pos += lpr) {
+                const uint32_t col = indices[pos];
+                if (EVENT) {
+                    if (is_event(x[col])) { if (HOMO) ++hits; else acc += data[pos]; }
+                } else {
+                    acc += (HOMO ? homo_w : data[pos]) * static_cast<T>(x[col]);
+                }
+            }
+        }
+        if (EVENT && HOMO) {
+            hits = group_sum(hits, static_cast<int>(lpr));
+            acc = static_cast<T>(static_cast<double>(hits) * static_cast<double>(homo_w));
+        } else {
+            acc = group_sum(acc, static_cast<int>(lpr));
+        }
+        if (live && sl == 0) y[row] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+// Optional CUDA events recorded around the scatter kernel of the transposed event product
+// (see bpl_profile_scatter_events); per host thread, off by default.
+thread_local cudaEvent_t g_profile_before = nullptr, g_profile_after = nullptr;
+
+inline int persistent_blocks(int blocks_per_sm, uint64_t work_warps) {
+    const uint64_t cap = static_cast<uint64_t>(sm_count()) * blocks_per_sm;
+    const uint64_t need = (work_warps + ROW_WARPS - 1) / ROW_WARPS;
+    return static_cast<int>(need < 1 ? 1 : (need < cap ? need : cap));
+}
+
+template<typename T, typename E, bool HOMO>
+void event_csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    const TwoUintOneBoolDescriptor *d = unpack<TwoUintOneBoolDescriptor>(opaque, opaque_len);
+    if (!d) return;
+    const uint32_t n_row = d->uint_x, n_col = d->uint_y;
+    const T *data = static_cast<const T *>(buffers[0]);
+    const uint32_t *indices = static_cast<const uint32_t *>(buffers[1]);
+    const uint32_t *indptr = static_cast<const uint32_t *>(buffers[2]);
+    const E *events = static_cast<const E *>(buffers[3]);
+    T *y = static_cast<T *>(buffers[4]);
+    const bool vec = aligned16(indices) && (HOMO || aligned16(data));
+
+    if (d->bool_x) {
+        if (n_col == 0) return;
+        uint32_t *ws = static_cast<uint32_t *>(buffers[5]);
+        if (ws == nullptr) {
+            set_status(BPL_ERR_ARGUMENT, "event_csr_matvec(transpose=True) needs a workspace buffer");
+            return;
+        }
+        uint32_t *counts = ws, *ids = ws + MAX_CHUNKS;
+        const ScanPlan p = plan_scan(n_row);
+        const uint64_t zero_blocks = (static_cast<uint64_t>(n_col) + SCAN_TILE - 1) / SCAN_TILE;
+        const uint64_t zero_cap = static_cast<uint64_t>(sm_count()) * 8;
+        const uint32_t scan_grid = static_cast<uint32_t>(
+            max(static_cast<uint64_t>(p.n_chunks), min(zero_blocks, zero_cap)));
+        scan_events_kernel<T, E><<<scan_grid, SCAN_THREADS, 0, stream>>>(
+            events, n_row, p.chunk, p.n_chunks, y, n_col, counts, ids);
+        if (!launch_ok()) return;
+        if (n_row == 0) return;
+        // one warp per work item; the grid is sized for the worst case (every row active) but capped
+        const int grid = persistent_blocks(4, static_cast<uint64_t>(n_row) * 16);
+        if (g_profile_before) cudaEventRecord(g_profile_before, stream);
+        if (vec)
+            row_scatter_kernel<T, HOMO, true, true><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
+        else
+            row_scatter_kernel<T, HOMO, true, false><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
+        if (g_profile_after) cudaEventRecord(g_profile_after, stream);
+        launch_ok();
+    } else {
+        if (n_row == 0) return;
+        const int grid = persistent_blocks(8, n_row);
+        if (vec)
+            row_gather_kernel<T, E, HOMO, true, true><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, events, n_row, y);
+        else
+            row_gather_kernel<T, E, HOMO, true, false><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, events, n_row, y);
+        launch_ok();
+    }
+}
+
+template<typename T, bool HOMO>
+void csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len,
+                     bool transpose, int vector_slot) {
+    const DoubleSizeDescriptor *d = unpack<DoubleSizeDescriptor>(opaque, opaque_len);
+    if (!d) return;
+    const uint32_t n_row = d->size_x, n_col = d->size_y;
+    const T *data = static_cast<const T *>(buffers[0]);
+    const uint32_t *indices = static_cast<const uint32_t *>(buffers[1]);
+    const uint32_t *indptr = static_cast<const uint32_t *>(buffers[2]);
+    const T *x = static_cast<const T *>(buffers[vector_slot]);
+    T *y = static_cast<T *>(buffers[vector_slot + 1]);
+    const bool vec = aligned16(indices) && (HOMO || aligned16(data));
+
+    if (transpose) {
+        if (n_col == 0) return;
+        if (cudaMemsetAsync(y, 0, sizeof(T) * static_cast<size_t>(n_col), stream) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        if (n_row == 0) return;
+        const int grid = persistent_blocks(4, static_cast<uint64_t>(n_row) * 16);
+        if (vec)
+            row_scatter_kernel<T, HOMO, false, true><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, x, n_row, 0, 0, nullptr, nullptr, y);
+        else
+            row_scatter_kernel<T, HOMO, false, false><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, x, n_row, 0, 0, nullptr, nullptr, y);
+    } else {
+        if (n_row == 0) return;
+        const int grid = persistent_blocks(8, n_row);
+        if (vec)
+            row_gather_kernel<T, T, HOMO, false, true><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, x, n_row, y);
+        else
+            row_gather_kernel<T, T, HOMO, false, false><<<grid, ROW_THREADS, 0, stream>>>(
+                indices, indptr, data, x, n_row, y);
+    }
+    launch_ok();
+}
+
+}  // namespace
+}  // namespace bpl
+
+using namespace bpl;
+
+extern "C" {
+
+void bpl_profile_scatter_events(void *before, void *after) {
+    g_profile_before = static_cast<cudaEvent_t>(before);
+    g_profile_after = static_cast<cudaEvent_t>(after);
+}
+
+size_t bpl_event_csr_workspace_bytes(uint32_t n_row, int transpose) {
+    return transpose ? scatter_workspace_bytes(n_row) : 0;
+}
+
+#define EVENT_CSR_TARGET(name, T, E, HOMO) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { event_csr_matvec_impl<T, E, HOMO>(s, b, o, n); }
+
+EVENT_CSR_TARGET(event_csr_matvec_homo_float_bool, float, uint8_t, true)
+EVENT_CSR_TARGET(event_csr_matvec_homo_float_float, float, float, true)
+EVENT_CSR_TARGET(event_csr_matvec_homo_double_bool, double, uint8_t, true)
+EVENT_CSR_TARGET(event_csr_matvec_homo_double_double, double, double, true)
+EVENT_CSR_TARGET(event_csr_matvec_heter_float_bool, float, uint8_t, false)
+EVENT_CSR_TARGET(event_csr_matvec_heter_float_float, float, float, false)
+EVENT_CSR_TARGET(event_csr_matvec_heter_double_bool, double, uint8_t, false)
+EVENT_CSR_TARGET(event_csr_matvec_heter_double_double, double, double, false)
+
+// The reference's scalar / vector / adaptive methods (lib/gpu_csr_matvec.cu) differ only in
+// how rows are mapped to threads; here all three names run the same kernel.  'adaptive'
+// carries its row_blocks operand at slot 3, which is ignored.
+#define CSR_TARGET(name, T, HOMO, TRANSPOSE, SLOT) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { csr_matvec_impl<T, HOMO>(s, b, o, n, TRANSPOSE, SLOT); }
+
+CSR_TARGET(csr_matvec_homo_scalar_float, float, true, false, 3)
+CSR_TARGET(csr_matvec_homo_scalar_double, double, true, false, 3)
+CSR_TARGET(csr_matvec_homo_vector_float, float, true, false, 3)
+CSR_TARGET(csr_matvec_homo_vector_double, double, true, false, 3)
+CSR_TARGET(csr_matvec_homo_adaptive_float, float, true, false, 4)
+CSR_TARGET(csr_matvec_homo_adaptive_double, double, true, false, 4)
+CSR_TARGET(csr_matvec_heter_scalar_float, float, false, false, 3)
+CSR_TARGET(csr_matvec_heter_scalar_double, double, false, false, 3)
+CSR_TARGET(csr_matvec_heter_vector_float, float, false, false, 3)
+CSR_TARGET(csr_matvec_heter_vector_double, double, false, false, 3)
+CSR_TARGET(csr_matvec_heter_adaptive_float, float, false, false, 4)
+CSR_TARGET(csr_matvec_heter_adaptive_double, double, false, false, 4)
+CSR_TARGET(csr_matvec_transpose_homo_float, float, true, true, 3)
+CSR_TARGET(csr_matvec_transpose_homo_double, double, true, true, 3)
+CSR_TARGET(csr_matvec_transpose_heter_float, float, false, true, 3)
+CSR_TARGET(csr_matvec_transpose_heter_double, double, false, true, 3)
+
+}  // extern "C"

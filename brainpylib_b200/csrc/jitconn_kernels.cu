@@ -1,0 +1,466 @@
+// Just-in-time connectivity products for sm_100a: the matrix is never stored, every row
+// (or column) regenerates its synapses from the stream `seed + index`.
+//   gpu_matvec{,_atomic}_prob_*_v2        replaces lib/gpu_jitconn_matvec{,_atomic}.cu
+//   gpu_event_matvec{,_atomic}_prob_*_v2  replaces lib/gpu_jitconn_event_matvec{,_atomic}.cu
+//   gpu_matmat_prob_prob_*_v1             replaces lib/gpu_jitconn_matmat.cu
+//
+// Generator scheme (must stay bit-identical to the reference, whose sampled connectivity is
+// the contract): cuRAND XORWOW, `curand_init(seed + i, 0, 0)`; position of the next synapse
+//     pos += (int) ceil( log(curand_uniform(&st)) / log_p )
+// with a float `log`, a float/double division carried out in double, `ceil`, and a
+// conversion to int (lib/gpu_jitconn_matvec.cu:99-106).  The weight of a synapse is drawn
+// after its position and before the next gap: uniform `(T)(u * w_range + w_min)`,
+// normal `(T)(n * w_sigma + w_mu)`, both evaluated in double (lib/gpu_jitconn_matvec.cu:243,386).
+// The same cuRAND device functions and the same expressions are used here, compiled
+// without fast-math, so the bits agree.
+#include <curand_kernel.h>
+
+#include "abi.h"
+#include "common.cuh"
+
+namespace bpl {
+namespace {
+
+enum { W_HOMO = 0, W_UNIFORM = 1, W_NORMAL = 2 };
+
+struct Stream {
+    curandState st;
+    double log_p;
+
+    __device__ __forceinline__ Stream(unsigned int stream_seed, double lp) : log_p(lp) {
+        curand_init(stream_seed, 0, 0, &st);
+    }
+    __device__ __forceinline__ int gap() { return (int) ceil(log(curand_uniform(&st)) / log_p); }
+    __device__ __forceinline__ unsigned int ugap() { return (unsigned int) ceil(log(curand_uniform(&st)) / log_p); }
+    template<typename T, int KIND>
+    __device__ __forceinline__ T weight(double w1, double w2) {
+        if (KIND == W_UNIFORM) return (T) (curand_uniform(&st) * w2 + w1);
+        if (KIND == W_NORMAL) return (T) (curand_normal(&st) * w2 + w1);
+        return T(1);
+    }
+};
+
+constexpr int JIT_THREADS = 256;
+
+// ------------------------------------------------------------------------------------------
+// Row-parallel (outdim_parallel = True): one thread owns one output row.
+// ------------------------------------------------------------------------------------------
+// Dense input: lib/gpu_jitconn_matvec.cu:84-112, :220-251, :363-394.
+template<typename T, int KIND>
+__global__ void __launch_bounds__(JIT_THREADS)
+jit_rows_dense_kernel(const T *__restrict__ vector, const unsigned int seed, const double log_p,
+                      const double w1, const double w2, const unsigned int num_row,
+                      const unsigned int num_col, T *__restrict__ out) {
+    const unsigned int row_i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row_i >= num_row) return;
+    Stream s(seed + row_i, log_p);
+    T sum = 0;
+    int pos = s.gap();
+    while (pos < num_col) {
+        if (KIND == W_HOMO) {
+            sum += vector[pos];
+        } else {
+            const T rand = s.template weight<T, KIND>(w1, w2);
+            sum += (vector[pos] * rand);
+        }
+        pos += s.gap();
+    }
+    out[row_i] = sum;
+}
+
+// Event input read straight from global memory: lib/gpu_jitconn_event_matvec.cu:81-108
+// (homogeneous: adds the event VALUE), :217-248, :365-396 (weight drawn for every synapse,
+// added when the event is truthy).
+template<typename T, typename E, int KIND>
+__global__ void __launch_bounds__(JIT_THREADS)
+jit_rows_event_kernel(const E *__restrict__ events, const unsigned int seed, const double log_p,
+                      const double w1, const double w2, const unsigned int num_row,
+                      const unsigned int num_col, T *__restrict__ out) {
+    const unsigned int row_i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row_i >= num_row) return;
+    Stream s(seed + row_i, log_p);
+    T sum = 0;
+    int pos = s.gap();
+    while (pos < num_col) {
+        if (KIND == W_HOMO) {
+            sum += events[pos];
+        } else {
+            const T rand = s.template weight<T, KIND>(w1, w2);
+            if (events[pos]) sum += rand;
+        }
+        pos += s.gap();
+    }
+    out[row_i] = sum;
+}
+
+// Event input held as a bitmask in shared memory (one bit per input neuron).  Used when only
+// the truthiness of an event matters (bool events, or weighted variants) and the mask fits:
+// 1e6 inputs = 125 KB.  One persistent block per SM packs the events once and then walks rows
+// `block + k * grid`; a random 1-byte gather from L2 per synapse becomes a shared-memory read.
+constexpr int MASK_THREADS = 1024;
+constexpr unsigned int MASK_MAX_BITS = 200u * 1024u * 8u;   // 200 KB of shared memory
+
+template<typename T, typename E, int KIND>
+__global__ void __launch_bounds__(MASK_THREADS, 1)
+jit_rows_event_mask_kernel(const E *__restrict__ events, const unsigned int seed, const double log_p,
+                           const double w1, const double w2, const unsigned int num_row,
+                           const unsigned int num_col, T *__restrict__ out) {
+    extern __shared__ uint32_t mask[];
+    const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned int n_words = (num_col + 31u) >> 5;
+    // pack: one ballot per 32 events, 8 loads in flight per lane
+    for (unsigned int w0 = warp * 8u; w0 < n_words; w0 += (MASK_THREADS / 32) * 8u) {
+        bool a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned int i = (w0 + j) * 32u + lane;
+            a[j] = (i < num_col) && is_event(events[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t bits = __ballot_sync(FULL_MASK, a[j]);
+            if (lane == 0 && w0 + j < n_words) mask[w0 + j] = bits;
+        }
+    }
+    __syncthreads();
+
+    for (unsigned int row_i = blockIdx.x * MASK_THREADS + threadIdx.x; row_i < num_row;
+         row_i += gridDim.x * MASK_THREADS) {
+        Stream s(seed + row_i, log_p);
+        T sum = 0;
+        int pos = s.gap();
+        while (pos < num_col) {
+            const bool hit = (mask[pos >> 5] >> (pos & 31)) & 1u;
+            if (KIND == W_HOMO) {
+                sum += (T) hit;   // bool event value: 0 or 1
+            } else {
+                const T rand = s.template weight<T, KIND>(w1, w2);
+                if (hit) sum += rand;
+            }
+            pos += s.gap();
+        }
+        out[row_i] = sum;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Column-parallel (outdim_parallel = False): one thread owns one input column and scatters.
+// ------------------------------------------------------------------------------------------
+// Dense input: lib/gpu_jitconn_matvec_atomic.cu:27-52, :82-110, :143-171.
+template<typename T, int KIND>
+__global__ void __launch_bounds__(JIT_THREADS)
+jit_cols_dense_kernel(const T *__restrict__ vector, const unsigned int seed, const double log_p,
+                      const double w1, const double w2, const unsigned int num_row,
+                      const unsigned int num_col, T *__restrict__ out) {
+    const unsigned int col_i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col_i >= num_col) return;
+    Stream s(seed + col_i, log_p);
+    const T v = vector[col_i];
+    int row_i = s.gap();
+    while (row_i < num_row) {
+        if (KIND == W_HOMO) {
+            atomicAdd(&out[row_i], v);
+        } else {
+            const T rand = s.template weight<T, KIND>(w1, w2);
+            atomicAdd(&out[row_i], v * rand);
+        }
+        row_i += s.gap();
+    }
+}
+
+// Event input: lib/gpu_jitconn_event_matvec_atomic.cu:30-58, :88-117, :150-178.  There every
+// column walks its stream and only the atomicAdd is conditional; a silent column therefore
+// contributes nothing and its stream is private, so it is skipped here.  Each block compacts
+// the firing columns of its chunk into shared memory and gives one thread to each of them.
+constexpr int COL_CHUNK = JIT_THREADS * 8;
+
+template<typename T, typename E, int KIND>
+__global__ void __launch_bounds__(JIT_THREADS)
+jit_cols_event_kernel(const E *__restrict__ events, const unsigned int seed, const double log_p,
+                      const double w1, const double w2, const unsigned int num_row,
+                      const unsigned int num_col, T *__restrict__ out) {
+    __shared__ unsigned int active[COL_CHUNK];
+    __shared__ unsigned int n_active;
+    if (threadIdx.x == 0) n_active = 0;
+    __syncthreads();
+    const unsigned long long base = static_cast<unsigned long long>(blockIdx.x) * COL_CHUNK;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const unsigned long long c = base + k * JIT_THREADS + threadIdx.x;
+        if (c < num_col && is_event(events[c])) active[atomicAdd(&n_active, 1u)] = static_cast<unsigned int>(c);
+    }
+    __syncthreads();
+    const unsigned int n = n_active;
+    for (unsigned int i = threadIdx.x; i < n; i += JIT_THREADS) {
+        const unsigned int col_i = active[i];
+        Stream s(seed + col_i, log_p);
+        int row_i = s.gap();
+        while (row_i < num_row) {
+            if (KIND == W_HOMO) {
+                atomicAdd(&out[row_i], T(1));
+            } else {
+                const T weight = s.template weight<T, KIND>(w1, w2);
+                atomicAdd(&out[row_i], weight);
+            }
+            row_i += s.gap();
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Y = X @ M, M just-in-time with one stream per output column
+// (lib/gpu_jitconn_matmat.cu:236-276 normal, :321-361 uniform).
+// ------------------------------------------------------------------------------------------
+// A thread owns one output column and 32 rows of X, as in the reference, and accumulates
+// `sum[i] += X[row_i][pos] * w` in synapse order (same bits).  What changes is where X comes
+// from: the reference reads X[(m_i + i) * k + pos] from global memory, one 32-byte sector per
+// float; here a K-tile of the 32 rows is staged TRANSPOSED in shared memory ([k][row]), so a
+// synapse reads 32 consecutive floats with 128-bit shared loads.  16-byte chunks of a tile row
+// are XOR-swizzled with the row number so that threads reading different rows spread over banks.
+constexpr int MM_THREADS = 512;
+constexpr int MM_ROWS = 32;
+
+template<typename T> struct MMTile;
+template<> struct MMTile<float> { static constexpr int KT = 512; static constexpr int CHUNKS = 8; };    // 64 KB
+template<> struct MMTile<double> { static constexpr int KT = 256; static constexpr int CHUNKS = 16; };  // 64 KB
+
+template<typename T, int KIND>
+__global__ void __launch_bounds__(MM_THREADS, 2)
+jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double log_p, const double w1,
+                  const double w2, const unsigned int m, const unsigned int k, const unsigned int n,
+                  T *__restrict__ Y) {
+    constexpr int KT = MMTile<T>::KT, CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS], chunk-swizzled
+
+    const unsigned long long n_i64 = static_cast<unsigned long long>(blockIdx.x) * MM_THREADS + threadIdx.x;
+    const bool live = n_i64 < n;
+    const unsigned int n_i = static_cast<unsigned int>(n_i64);
+    const unsigned int m_i = blockIdx.y * MM_ROWS;
+    const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    curandState st;
+    unsigned int pos = 0xffffffffu;
+    if (live) {
+        curand_init(seed + n_i, 0, 0, &st);
+        pos = (unsigned int) ceil(log(curand_uniform(&st)) / log_p);
+    }
+    T sum[MM_ROWS];
+#pragma unroll
+    for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
+
+    for (unsigned int k0 = 0; k0 < k; k0 += KT) {
+        // stage X[m_i .. m_i+31][k0 .. k0+KT) transposed; a warp reads along k (coalesced)
+        for (unsigned int r = warp; r < MM_ROWS; r += MM_THREADS / 32) {
+            const bool row_ok = m_i + r < m;
+            const T *src = X + static_cast<size_t>(m_i + r) * k;
+            for (unsigned int kk = lane; kk < KT; kk += 32) {
+                const T v = (row_ok && k0 + kk < k) ? src[k0 + kk] : T(0);
+                const unsigned int chunk = (r / PER_CHUNK) ^ (kk & (CHUNKS - 1));
+                tile[kk * MM_ROWS + chunk * PER_CHUNK + (r % PER_CHUNK)] = v;
+            }
+        }
+        __syncthreads();
+        const unsigned int k_end = min(k0 + KT, k);
+        while (pos < k_end) {
+            T rand;
+            if (KIND == W_NORMAL) rand = (T) (curand_normal(&st) * w2 + w1);
+            else rand = (T) (curand_uniform(&st) * w2 + w1);
+            const unsigned int kk = pos - k0;
+            const T *row = tile + kk * MM_ROWS;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const unsigned int chunk = c ^ (kk & (CHUNKS - 1));
+                if (sizeof(T) == 4) {
+                    const float4 x = *reinterpret_cast<const float4 *>(row + chunk * PER_CHUNK);
+                    sum[c * 4 + 0] += (x.x * rand);
+                    sum[c * 4 + 1] += (x.y * rand);
+                    sum[c * 4 + 2] += (x.z * rand);
+                    sum[c * 4 + 3] += (x.w * rand);
+                } else {
+                    const double2 x = *reinterpret_cast<const double2 *>(row + chunk * PER_CHUNK);
+                    sum[c * 2 + 0] += (x.x * rand);
+                    sum[c * 2 + 1] += (x.y * rand);
+                }
+            }
+            pos += (unsigned int) ceil(log(curand_uniform(&st)) / log_p);
+        }
+        __syncthreads();
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < MM_ROWS; ++i)
+            if (m_i + i < m) Y[static_cast<size_t>(m_i + i) * n + n_i] = sum[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+struct JitArgs {
+    unsigned int n_row, n_col, seed;
+    double log_p, w1, w2;
+};
+
+template<int KIND>
+inline bool unpack_jit(const char *opaque, size_t opaque_len, JitArgs &a) {
+    if (KIND == W_HOMO) {
+        const JITConnProbHomoDescriptor *d = unpack<JITConnProbHomoDescriptor>(opaque, opaque_len);
+        if (!d) return false;
+        a = JitArgs{d->n_row, d->n_col, d->seed, d->prob, 0.0, 0.0};
+    } else {
+        const JITConnProbWeightedDescriptor *d = unpack<JITConnProbWeightedDescriptor>(opaque, opaque_len);
+        if (!d) return false;
+        a = JitArgs{d->n_row, d->n_col, d->seed, d->prob, d->w1, d->w2};
+    }
+    return true;
+}
+
+inline unsigned int blocks_for(unsigned int n, unsigned int per_block) {
+    return static_cast<unsigned int>((static_cast<unsigned long long>(n) + per_block - 1) / per_block);
+}
+
+template<typename T, int KIND, bool ROWS>
+void jit_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    JitArgs a;
+    if (!unpack_jit<KIND>(opaque, opaque_len, a)) return;
+    const T *vector = static_cast<const T *>(buffers[0]);
+    T *y = static_cast<T *>(buffers[1]);
+    if (a.n_row == 0) return;
+    if (ROWS) {
+        jit_rows_dense_kernel<T, KIND><<<blocks_for(a.n_row, JIT_THREADS), JIT_THREADS, 0, stream>>>(
+            vector, a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col, y);
+    } else {
+        if (cudaMemsetAsync(y, 0, sizeof(T) * static_cast<size_t>(a.n_row), stream) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        if (a.n_col == 0) return;
+        jit_cols_dense_kernel<T, KIND><<<blocks_for(a.n_col, JIT_THREADS), JIT_THREADS, 0, stream>>>(
+            vector, a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col, y);
+    }
+    launch_ok();
+}
+
+template<typename T, typename E, int KIND>
+bool enable_mask_kernel(size_t bytes) {
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        if (cudaFuncSetAttribute(jit_rows_event_mask_kernel<T, E, KIND>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(MASK_MAX_BITS / 8)) != cudaSuccess) {
+            launch_ok();
+            return false;
+        }
+        configured_device = dev;
+    }
+    (void) bytes;
+    return true;
+}
+
+template<typename T, typename E, int KIND, bool ROWS>
+void jit_event_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    JitArgs a;
+    if (!unpack_jit<KIND>(opaque, opaque_len, a)) return;
+    const E *events = static_cast<const E *>(buffers[0]);
+    T *y = static_cast<T *>(buffers[1]);
+    if (a.n_row == 0) return;
+    if (ROWS) {
+        // the bitmask holds truthiness only: enough unless a homogeneous product must add float event values
+        const bool truth_only = (KIND != W_HOMO) || (sizeof(E) == 1);
+        const bool big_enough = static_cast<unsigned long long>(a.n_row) >= 4ull * MASK_THREADS;
+        if (truth_only && big_enough && a.n_col <= MASK_MAX_BITS) {
+            const size_t bytes = static_cast<size_t>((a.n_col + 31u) >> 5) * 4;
+            if (!enable_mask_kernel<T, E, KIND>(bytes)) return;
+            const unsigned int grid = min(static_cast<unsigned int>(sm_count()), blocks_for(a.n_row, MASK_THREADS));
+            jit_rows_event_mask_kernel<T, E, KIND><<<grid, MASK_THREADS, bytes, stream>>>(
+                events, a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col, y);
+        } else {
+            jit_rows_event_kernel<T, E, KIND><<<blocks_for(a.n_row, JIT_THREADS), JIT_THREADS, 0, stream>>>(
+                events, a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col, y);
+        }
+    } else {
+        if (cudaMemsetAsync(y, 0, sizeof(T) * static_cast<size_t>(a.n_row), stream) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        if (a.n_col == 0) return;
+        jit_cols_event_kernel<T, E, KIND><<<blocks_for(a.n_col, COL_CHUNK), JIT_THREADS, 0, stream>>>(
+            events, a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col, y);
+    }
+    launch_ok();
+}
+
+template<typename T, int KIND>
+void jit_matmat_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    const MatMatJITProbDescriptor1 *d = unpack<MatMatJITProbDescriptor1>(opaque, opaque_len);
+    if (!d) return;
+    const T *X = static_cast<const T *>(buffers[0]);
+    T *Y = static_cast<T *>(buffers[1]);
+    if (d->m == 0 || d->n == 0) return;
+    const unsigned int gy = blocks_for(d->m, MM_ROWS);
+    if (gy > 65535u) {
+        set_status(BPL_ERR_ARGUMENT, "matmat: more than 65535 * 32 rows in the dense operand");
+        return;
+    }
+    constexpr size_t smem = static_cast<size_t>(MMTile<T>::KT) * MM_ROWS * sizeof(T);
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        if (cudaFuncSetAttribute(jit_matmat_kernel<T, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        configured_device = dev;
+    }
+    const dim3 grid(blocks_for(d->n, MM_THREADS), gy);
+    jit_matmat_kernel<T, KIND><<<grid, MM_THREADS, smem, stream>>>(
+        X, d->seed, d->log_p, d->w1, d->w2, d->m, d->k, d->n, Y);
+    launch_ok();
+}
+
+}  // namespace
+}  // namespace bpl
+
+using namespace bpl;
+
+extern "C" {
+
+#define JIT_MATVEC(name, T, KIND, ROWS) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_matvec_impl<T, KIND, ROWS>(s, b, o, n); }
+#define JIT_MATVEC_ALL(kind, KIND)                                           \
+    JIT_MATVEC(gpu_matvec_prob_##kind##_v2_float, float, KIND, true)          \
+    JIT_MATVEC(gpu_matvec_prob_##kind##_v2_double, double, KIND, true)        \
+    JIT_MATVEC(gpu_matvec_atomic_prob_##kind##_v2_float, float, KIND, false)  \
+    JIT_MATVEC(gpu_matvec_atomic_prob_##kind##_v2_double, double, KIND, false)
+JIT_MATVEC_ALL(homo, W_HOMO)
+JIT_MATVEC_ALL(uniform, W_UNIFORM)
+JIT_MATVEC_ALL(normal, W_NORMAL)
+
+#define JIT_EVENT(name, T, E, KIND, ROWS) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_event_matvec_impl<T, E, KIND, ROWS>(s, b, o, n); }
+#define JIT_EVENT_ALL(kind, KIND)                                                               \
+    JIT_EVENT(gpu_event_matvec_prob_##kind##_v2_float_bool, float, bool, KIND, true)             \
+    JIT_EVENT(gpu_event_matvec_prob_##kind##_v2_float_float, float, float, KIND, true)           \
+    JIT_EVENT(gpu_event_matvec_prob_##kind##_v2_double_bool, double, bool, KIND, true)           \
+    JIT_EVENT(gpu_event_matvec_prob_##kind##_v2_double_double, double, double, KIND, true)       \
+    JIT_EVENT(gpu_event_matvec_atomic_prob_##kind##_v2_float_bool, float, bool, KIND, false)     \
+    JIT_EVENT(gpu_event_matvec_atomic_prob_##kind##_v2_float_float, float, float, KIND, false)   \
+    JIT_EVENT(gpu_event_matvec_atomic_prob_##kind##_v2_double_bool, double, bool, KIND, false)   \
+    JIT_EVENT(gpu_event_matvec_atomic_prob_##kind##_v2_double_double, double, double, KIND, false)
+JIT_EVENT_ALL(homo, W_HOMO)
+JIT_EVENT_ALL(uniform, W_UNIFORM)
+JIT_EVENT_ALL(normal, W_NORMAL)
+
+#define JIT_MATMAT(name, T, KIND) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_matmat_impl<T, KIND>(s, b, o, n); }
+JIT_MATMAT(gpu_matmat_prob_prob_normal_float_v1, float, W_NORMAL)
+JIT_MATMAT(gpu_matmat_prob_prob_normal_double_v1, double, W_NORMAL)
+JIT_MATMAT(gpu_matmat_prob_prob_uniform_float_v1, float, W_UNIFORM)
+JIT_MATMAT(gpu_matmat_prob_prob_uniform_double_v1, double, W_UNIFORM)
+
+}  // extern "C"

@@ -1,0 +1,183 @@
+/*
+ * brainpylib_b200 — C ABI of the B200 synaptic-propagation library.
+ *
+ * Every operator is an XLA GPU custom-call target with the legacy (API version 0)
+ * signature the reference library uses (lib/gpu_event_csr_matvec.cuh:14-15):
+ *
+ *     void target(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len);
+ *
+ * `buffers` holds device pointers: the operands in call order, then the outputs,
+ * then (only where stated) ONE trailing workspace buffer that the caller owns.
+ * `opaque` is a packed descriptor, byte-identical to the reference's
+ * (lib/kernel_helper_descriptor.cuh:49-144).  A target only enqueues work on
+ * `stream`; it never synchronises, allocates, frees or keeps a pointer.  Outputs
+ * may arrive uninitialised.  Errors never cross the boundary as C++ exceptions
+ * (the reference throws, lib/kernel_helpers.h:36-38): they are recorded per
+ * host thread and read with bpl_last_status().
+ *
+ * The C symbol of a target is the registration name the reference uses in
+ * lib/gpu_ops.cc:28-174, so a registry built from bpl_registration_*() is a
+ * drop-in for `gpu_ops.registrations()`.
+ */
+#ifndef BRAINPYLIB_B200_H_
+#define BRAINPYLIB_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *bpl_stream_t; /* == cudaStream_t */
+typedef void (*bpl_custom_call_t)(bpl_stream_t stream, void **buffers, const char *opaque, size_t opaque_len);
+
+/* ---- status (replaces the reference's C++ exceptions: lib/kernel_helpers.h:34-40,
+ *      lib/kernel_helpers_gpu.cuh:15-19) ------------------------------------------------- */
+enum {
+    BPL_OK = 0,
+    BPL_ERR_OPAQUE_SIZE = 1,  /* "Invalid opaque object size" */
+    BPL_ERR_CUDA = 2,         /* launch / runtime error, message = cudaGetErrorString */
+    BPL_ERR_ARGUMENT = 3,     /* a size the kernels cannot take */
+    BPL_ERR_TOO_LARGE = 4     /* beyond the fixed capacity of a no-allocation entry point */
+};
+/* Status of the last target called on THIS host thread; copies the message (may be NULL). */
+int bpl_last_status(char *message, size_t capacity);
+void bpl_clear_status(void);
+
+/* ---- registry (replaces Registrations() of lib/gpu_ops.cc:24-177) ------------------------- */
+int bpl_registration_count(void);
+const char *bpl_registration_name(int i);
+bpl_custom_call_t bpl_registration_target(int i);
+bpl_custom_call_t bpl_find_target(const char *name); /* NULL when unknown */
+
+/* ---- descriptor builders (replace build_*_descriptor of lib/kernel_helper_descriptor.cu:13-102,
+ *      lib/gpu_event_sum.cu, lib/gpu_atomic_sum.cu, lib/gpu_atomic_prod.cu).  Each writes the packed
+ *      struct to `out` (capacity `cap` bytes) and returns its size, or 0 when `cap` is too small.
+ *      As in the reference, real-valued fields arrive as `float` and are stored as `double`. ---- */
+size_t bpl_build_twouint_onebool_descriptor(uint32_t uint_x, uint32_t uint_y, int bool_x, void *out, size_t cap);
+size_t bpl_build_double_size_descriptor(uint32_t size_x, uint32_t size_y, void *out, size_t cap);
+size_t bpl_build_jitconn_prob_homo_descriptor(uint32_t n_row, uint32_t n_col, uint32_t seed, float prob,
+                                              void *out, size_t cap);
+size_t bpl_build_jitconn_prob_uniform_descriptor(uint32_t n_row, uint32_t n_col, uint32_t seed, float prob,
+                                                 float w_min, float w_range, void *out, size_t cap);
+size_t bpl_build_jitconn_prob_normal_descriptor(uint32_t n_row, uint32_t n_col, uint32_t seed, float prob,
+                                                float w_mu, float w_sigma, void *out, size_t cap);
+size_t bpl_build_matmat_jit_prob_descriptor1(uint32_t m, uint32_t k, uint32_t n, uint32_t seed, float log_p,
+                                             float w1, float w2, void *out, size_t cap);
+size_t bpl_build_csr_event_sum_descriptor(uint32_t pre_size, uint32_t post_size, void *out, size_t cap);
+size_t bpl_build_coo_event_sum_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
+size_t bpl_build_coo_atomic_sum_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
+size_t bpl_build_coo_atomic_prod_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
+size_t bpl_build_nonzero_descriptor(uint32_t event_size, uint32_t batch_size, void *out, size_t cap);
+
+/* ---- workspace -------------------------------------------------------------------------
+ * Bytes of the trailing workspace buffer a target needs for the given opaque descriptor
+ * (0 = the target takes no workspace buffer).  The workspace is scratch: its contents
+ * need not be initialised and are undefined afterwards.  Under XLA it is declared as one
+ * more (discarded) uint8 output, the way the reference's `event_info` returns a second
+ * array (brainpylib/_src/event_ops/event_info_collection.py:115-122). */
+size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t opaque_len);
+
+/* ---- profiling hook (no counterpart in the reference) -------------------------------------
+ * When both are non-NULL cudaEvent_t handles, every later event_csr_matvec_* call with
+ * transpose=true made by THIS host thread records `before` / `after` on its stream directly
+ * around its scatter kernel, so that kernel can be timed on its own.  NULL switches it off. */
+void bpl_profile_scatter_events(void *before, void *after);
+
+/* ---- targets ----------------------------------------------------------------------------
+ * E = events element: bool (1 byte) or the float type of the op; T = float | double.
+ *
+ * event_csr_matvec_{homo,heter}_{float_bool,float_float,double_bool,double_double}
+ *   replaces lib/gpu_event_csr_matvec.cu:148-217 (registered lib/gpu_ops.cc:95-104)
+ *   opaque  TwoUintOneBoolDescriptor{n_row, n_col, transpose}
+ *   buffers [data T(1|nse), indices u32(nse), indptr u32(n_row+1), events E, y T, workspace]
+ *   workspace: bpl_workspace_bytes() bytes when transpose, none otherwise (slot ignored).
+ *
+ * csr_matvec_{homo,heter}_{scalar,vector,adaptive}_{float,double}
+ *   replaces lib/gpu_csr_matvec.cu:84-141,195-246,505-560 (lib/gpu_ops.cc:79-92); the three
+ *   method names run the same kernel; 'adaptive' ignores its extra row_blocks operand.
+ *   opaque  DoubleSizeDescriptor{n_row, n_col}
+ *   buffers [data, indices, indptr, vector T(n_col), y T(n_row)]   (adaptive: row_blocks at 3)
+ * csr_matvec_transpose_{homo,heter}_{float,double}
+ *   y = A^T x; replaces the jaxlib cuSPARSE lowering the reference's AD rules call
+ *   (brainpylib/_src/sparse_ops/cusparse_matvec.py:266-278; math :195-212).
+ *   opaque  DoubleSizeDescriptor{n_row, n_col}; buffers [data, indices, indptr, vector T(n_row), y T(n_col)]
+ *
+ * gpu_matvec{,_atomic}_prob_{homo,uniform,normal}_v2_{float,double}
+ *   replaces lib/gpu_jitconn_matvec.cu:115-139,254-281,397-424 and
+ *   lib/gpu_jitconn_matvec_atomic.cu:55-78,113-139,174-200 (lib/gpu_ops.cc:151-164)
+ *   opaque  JITConnProb{Homo,Uniform,Normal}Descriptor; buffers [vector T(n_col), y T(n_row)]
+ * gpu_event_matvec{,_atomic}_prob_{homo,uniform,normal}_v2_{float_bool,float_float,double_bool,double_double}
+ *   replaces lib/gpu_jitconn_event_matvec.cu:111-135,251-278,399-426 and
+ *   lib/gpu_jitconn_event_matvec_atomic.cu:61-85,120-147,181-208 (lib/gpu_ops.cc:115-140)
+ *   opaque  as above; buffers [events E(n_col), y T(n_row)]
+ * gpu_matmat_prob_prob_{normal,uniform}_{float,double}_v1
+ *   replaces lib/gpu_jitconn_matmat.cu:279-317,364-402 (lib/gpu_ops.cc:171-174)
+ *   opaque  MatMatJITProbDescriptor1{m,k,n,seed,log_p,w1,w2}; buffers [X T(m,k), Y T(m,n)] row-major
+ *
+ * gpu_csr_event_sum_{homo,heter}_{f32,f64}_{i32,i64}   replaces lib/gpu_event_sum.cu:50-117
+ *   opaque {pre_size, post_size}; buffers [events bool, indices I, indptr I, values T, y T]
+ * gpu_coo_event_sum_{homo,heter}_{f32,f64}_{i32,i64}   replaces lib/gpu_event_sum.cu:140-206
+ *   opaque {conn_size, post_size}; buffers [events bool, pre_ids I, post_ids I, values T, y T]
+ * gpu_coo_atomic_sum_{homo,heter}_{f32,f64}_{i32,i64}  replaces lib/gpu_atomic_sum.cu:39-97
+ * gpu_coo_atomic_prod_{homo,heter}_{f32,f64}_{i32,i64} replaces lib/gpu_atomic_prod.cu:39-97
+ *   opaque {conn_size, post_size}; buffers homo [values T(1), post_ids I, y T]
+ *                                          heter [values T, pre_ids I, post_ids I, y T]
+ *   y[post[i]] op= values[pre[i]].  The heter operand order is the one the reference's Python
+ *   side passes (brainpylib/_src/compat/atomic_sum.py:128-131) and its CPU kernel reads
+ *   (lib/cpu_atomic_sum.cc:8-10); the reference's CUDA wrapper reads the two id arrays the other
+ *   way round (lib/gpu_atomic_sum.cu:86-87), which is not followed.  "prod" multiplies from 1.0
+ *   as lib/cpu_atomic_prod.cc:6-43 does (the reference's CUDA "prod" adds).
+ */
+#define BPL_DECLARE_TARGET(name) \
+    void name(bpl_stream_t stream, void **buffers, const char *opaque, size_t opaque_len)
+
+#define BPL_FOR_EACH_TE(X, stem) X(stem##_float_bool) X(stem##_float_float) X(stem##_double_bool) X(stem##_double_double)
+#define BPL_FOR_EACH_T(X, stem) X(stem##_float) X(stem##_double)
+#define BPL_FOR_EACH_FI(X, stem) X(stem##_f32_i32) X(stem##_f32_i64) X(stem##_f64_i32) X(stem##_f64_i64)
+
+#define BPL_FOR_EACH_TARGET(X)                                      \
+    BPL_FOR_EACH_TE(X, event_csr_matvec_homo)                       \
+    BPL_FOR_EACH_TE(X, event_csr_matvec_heter)                      \
+    BPL_FOR_EACH_T(X, csr_matvec_homo_scalar)                       \
+    BPL_FOR_EACH_T(X, csr_matvec_homo_vector)                       \
+    BPL_FOR_EACH_T(X, csr_matvec_homo_adaptive)                     \
+    BPL_FOR_EACH_T(X, csr_matvec_heter_scalar)                      \
+    BPL_FOR_EACH_T(X, csr_matvec_heter_vector)                      \
+    BPL_FOR_EACH_T(X, csr_matvec_heter_adaptive)                    \
+    BPL_FOR_EACH_T(X, csr_matvec_transpose_homo)                    \
+    BPL_FOR_EACH_T(X, csr_matvec_transpose_heter)                   \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_homo_v2)                      \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_uniform_v2)                   \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_normal_v2)                    \
+    BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_homo_v2)               \
+    BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_uniform_v2)            \
+    BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_normal_v2)             \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_homo_v2)               \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_uniform_v2)            \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_normal_v2)             \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_atomic_prob_homo_v2)        \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_atomic_prob_uniform_v2)     \
+    BPL_FOR_EACH_TE(X, gpu_event_matvec_atomic_prob_normal_v2)      \
+    X(gpu_matmat_prob_prob_normal_float_v1)                         \
+    X(gpu_matmat_prob_prob_normal_double_v1)                        \
+    X(gpu_matmat_prob_prob_uniform_float_v1)                        \
+    X(gpu_matmat_prob_prob_uniform_double_v1)                       \
+    BPL_FOR_EACH_FI(X, gpu_csr_event_sum_homo)                      \
+    BPL_FOR_EACH_FI(X, gpu_csr_event_sum_heter)                     \
+    BPL_FOR_EACH_FI(X, gpu_coo_event_sum_homo)                      \
+    BPL_FOR_EACH_FI(X, gpu_coo_event_sum_heter)                     \
+    BPL_FOR_EACH_FI(X, gpu_coo_atomic_sum_homo)                     \
+    BPL_FOR_EACH_FI(X, gpu_coo_atomic_sum_heter)                    \
+    BPL_FOR_EACH_FI(X, gpu_coo_atomic_prod_homo)                    \
+    BPL_FOR_EACH_FI(X, gpu_coo_atomic_prod_heter)
+
+#define BPL_DECLARE_ONE(name) BPL_DECLARE_TARGET(name);
+BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
+#undef BPL_DECLARE_ONE
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRAINPYLIB_B200_H_ */

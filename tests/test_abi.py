@@ -1,0 +1,160 @@
+"""Host-side checks of the C ABI: the library loads, exports every symbol the public
+header declares, packs descriptors byte-identically to the reference's structs
+(lib/kernel_helper_descriptor.cuh:49-144), and reports errors without raising across the
+boundary.  No kernel is launched here."""
+import ctypes
+import os
+import re
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, 'include', 'brainpylib_b200.h')
+
+
+def declared_symbols():
+  """Function names declared in the header, with the target list macro expanded by the preprocessor."""
+  text = ''.join(line for line in open(HEADER) if not line.lstrip().startswith('#include'))
+  out = subprocess.run(['gcc', '-E', '-P', '-x', 'c', '-'], input=text, check=True, capture_output=True,
+                       text=True).stdout
+  names = re.findall(r'\b(\w+)\s*\([^;{()]*\)\s*;', out)
+  return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+  from brainpylib_b200 import _lib
+  lib = _lib.lib()
+  names = declared_symbols()
+  assert len(names) > 100
+  for n in names:
+    if n == 'bpl_custom_call_t':
+      continue
+    assert hasattr(lib, n), f'{n} is declared in include/brainpylib_b200.h but not exported'
+
+
+def test_registrations_are_xla_capsules():
+  from brainpylib_b200 import gpu_ops
+  regs = gpu_ops.registrations()
+  assert len(regs) == len(gpu_ops.target_names()) == 96
+  get_name = ctypes.pythonapi.PyCapsule_GetName
+  get_name.restype = ctypes.c_char_p
+  get_name.argtypes = [ctypes.py_object]
+  get_ptr = ctypes.pythonapi.PyCapsule_GetPointer
+  get_ptr.restype = ctypes.c_void_p
+  get_ptr.argtypes = [ctypes.py_object, ctypes.c_char_p]
+  for name, capsule in regs.items():
+    assert get_name(capsule) == b'xla._CUSTOM_CALL_TARGET'
+    assert get_ptr(capsule, b'xla._CUSTOM_CALL_TARGET')
+  # the names the reference's Python layer asks for (lib/gpu_ops.cc:79-174)
+  for n in ['event_csr_matvec_homo_float_bool', 'event_csr_matvec_heter_double_double',
+            'csr_matvec_heter_vector_float', 'csr_matvec_homo_adaptive_double',
+            'gpu_event_matvec_prob_uniform_v2_float_bool', 'gpu_event_matvec_atomic_prob_normal_v2_double_double',
+            'gpu_matvec_prob_homo_v2_float', 'gpu_matvec_atomic_prob_normal_v2_double',
+            'gpu_matmat_prob_prob_normal_float_v1', 'gpu_matmat_prob_prob_uniform_double_v1',
+            'gpu_csr_event_sum_homo_f32_i32', 'gpu_coo_event_sum_heter_f64_i64',
+            'gpu_coo_atomic_sum_heter_f32_i32', 'gpu_coo_atomic_prod_homo_f64_i64']:
+    assert n in regs, n
+
+
+def test_descriptor_layouts():
+  from brainpylib_b200 import gpu_ops as g
+  d = g.build_twouint_onebool_descriptor(7, 9, True)
+  assert len(d) == 12 and struct.unpack('<II?3x', d) == (7, 9, True)
+  d = g.build_double_size_descriptor(5, 6)
+  assert len(d) == 8 and struct.unpack('<II', d) == (5, 6)
+  p = float(np.log(1 - 0.001))
+  d = g.build_jitconn_prob_homo_descriptor(10, 20, 42, p)
+  assert len(d) == 24
+  n_row, n_col, seed, prob = struct.unpack('<III4xd', d)
+  assert (n_row, n_col, seed) == (10, 20, 42)
+  # the builder takes a float: the double field holds the float32-rounded value
+  assert prob == float(np.float32(p)) and prob != p
+  for build in (g.build_jitconn_prob_uniform_descriptor, g.build_jitconn_prob_normal_descriptor):
+    d = build(1, 2, 3, p, -0.1, 0.2)
+    assert len(d) == 40
+    assert struct.unpack('<III4xddd', d) == (1, 2, 3, float(np.float32(p)), float(np.float32(-0.1)),
+                                             float(np.float32(0.2)))
+  d = g.build_matmat_jit_prob_descriptor1(256, 65536, 65536, 7, p, 0., 0.01)
+  assert len(d) == 40
+  assert struct.unpack('<IIIIddd', d) == (256, 65536, 65536, 7, float(np.float32(p)), 0., float(np.float32(0.01)))
+  for build in (g.build_csr_event_sum_descriptor, g.build_coo_event_sum_descriptor,
+                g.build_coo_atomic_sum_descriptor, g.build_coo_atomic_prod_descriptor, g.build_nonzero_descriptor):
+    assert struct.unpack('<II', build(11, 12)) == (11, 12)
+  # seeds wrap to 32 bits like the reference's `unsigned int` parameter
+  assert struct.unpack('<III4xd', g.build_jitconn_prob_homo_descriptor(1, 1, 2 ** 32 + 5, 0.))[2] == 5
+
+
+def test_wrong_opaque_size_sets_status_and_launches_nothing():
+  """The reference throws std::runtime_error("Invalid opaque object size") (lib/kernel_helpers.h:36-38);
+  here the call returns and the status says so.  The size check precedes any CUDA call."""
+  from brainpylib_b200 import _lib
+  lib = _lib.lib()
+  lib.bpl_clear_status()
+  fn = _lib.target('event_csr_matvec_homo_float_bool')
+  bufs = (ctypes.c_void_p * 6)()
+  fn(None, bufs, b'\x00' * 5, 5)
+  msg = ctypes.create_string_buffer(256)
+  assert lib.bpl_last_status(msg, 256) == 1
+  assert msg.value == b'Invalid opaque object size'
+  with pytest.raises(RuntimeError, match='Invalid opaque object size'):
+    _lib.check_status()
+  assert lib.bpl_last_status(None, 0) == 0
+  for name in ('csr_matvec_heter_vector_float', 'gpu_matvec_prob_homo_v2_float',
+               'gpu_event_matvec_prob_normal_v2_float_bool', 'gpu_matmat_prob_prob_normal_float_v1',
+               'gpu_coo_atomic_sum_homo_f32_i32'):
+    _lib.target(name)(None, bufs, b'', 0)
+    assert lib.bpl_last_status(None, 0) == 1
+    lib.bpl_clear_status()
+
+
+def test_workspace_query():
+  from brainpylib_b200 import _lib, gpu_ops
+  t = gpu_ops.build_twouint_onebool_descriptor(1_000_000, 1_000_000, True)
+  f = gpu_ops.build_twouint_onebool_descriptor(1_000_000, 1_000_000, False)
+  assert _lib.workspace_bytes('event_csr_matvec_heter_float_float', t) == (1024 + 1_000_000) * 4
+  assert _lib.workspace_bytes('event_csr_matvec_heter_float_float', f) == 0
+  assert _lib.workspace_bytes('csr_matvec_heter_vector_float', gpu_ops.build_double_size_descriptor(3, 4)) == 0
+
+
+def test_unknown_target_and_cpu_tensors_fail_loudly():
+  import torch
+  import brainpylib_b200 as b
+  from brainpylib_b200 import _lib
+  with pytest.raises(b.GPUOperatorNotFound):
+    _lib.target('no_such_target')
+  if not torch.cuda.is_available():
+    with pytest.raises(b.GPUOperatorNotFound):   # no CPU fallback
+      b.event_csr_matvec(0.6, torch.zeros(3, dtype=torch.int32), torch.tensor([0, 1, 3], dtype=torch.int32),
+                         torch.tensor([True, False]), shape=(2, 4), transpose=True)
+    with pytest.raises(b.GPUOperatorNotFound):
+      b.matvec_prob_conn_homo_weight(torch.zeros(4), 1., conn_prob=0.1, shape=(2, 4), seed=1)
+
+
+def test_argument_checks_match_reference():
+  """Errors raised before any device work (brainpylib/_src/event_ops/event_csr_matvec.py:75-99,
+  brainpylib/_src/sparse_ops/sparse_csr_matvec.py:71-83, brainpylib/_src/jitconn_ops/matmat.py:171-174)."""
+  import torch
+  import brainpylib_b200 as b
+  idx = torch.zeros(3, dtype=torch.int32)
+  ptr = torch.tensor([0, 1, 3], dtype=torch.int32)
+  with pytest.raises(ValueError, match='size of data'):
+    b.event_csr_matvec(torch.zeros(2), idx, ptr, torch.zeros(2, dtype=torch.bool), shape=(2, 4), transpose=True)
+  with pytest.raises(ValueError, match='int32 or uint32'):
+    b.event_csr_matvec(1., idx.to(torch.int64), ptr, torch.zeros(2, dtype=torch.bool), shape=(2, 4), transpose=True)
+  with pytest.raises(ValueError, match='Shape mismatch, vec'):
+    b.event_csr_matvec(1., idx, ptr, torch.zeros(4, dtype=torch.bool), shape=(2, 4), transpose=True)
+  with pytest.raises(ValueError, match='Shape mismatch, mat'):
+    b.event_csr_matvec(1., idx, ptr, torch.zeros(2, dtype=torch.bool), shape=(2, 4), transpose=False)
+  with pytest.raises(ValueError, match='Only support methods'):
+    b.csr_matvec(torch.zeros(3), idx, ptr, torch.zeros(4), shape=(2, 4), method='fancy')
+  with pytest.raises(TypeError, match='types of data and vector'):
+    b.csr_matvec(torch.zeros(3), idx, ptr, torch.zeros(4, dtype=torch.float64), shape=(2, 4))
+  with pytest.raises(ValueError, match='Seed cannot be none'):
+    b.matmat_prob_conn_normal_weight(torch.zeros(2, 4), w_mu=0., w_sigma=1., conn_prob=0.1, shape=(4, 5))
+  with pytest.raises(ValueError, match='Shape mismatch, X'):
+    b.matmat_prob_conn_normal_weight(torch.zeros(2, 3), w_mu=0., w_sigma=1., conn_prob=0.1, shape=(4, 5), seed=1)
+  with pytest.raises(ValueError, match='1D vector'):
+    b.event_matvec_prob_conn_homo_weight(torch.zeros(2, 2), 1., conn_prob=0.1, shape=(2, 2), seed=1)

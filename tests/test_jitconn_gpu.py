@@ -1,0 +1,264 @@
+"""GPU parity of the just-in-time-connectivity operators.
+
+Bitwise oracle: the reference's own CUDA kernels (lib/gpu_jitconn_*.cu compiled for sm_100a
+into oracle/_ref/libref_gpu.so) on the same inputs and descriptors.  Row-parallel outputs
+must be bit-identical (same streams, same per-row summation order); column-parallel outputs
+are sums of atomics and are compared with rtol 1e-5 / atol 1e-5 * expected in-degree, except
+homogeneous event products, which are integer counts and exact.
+
+Second check: the CPU oracle (oracle/jitconn_oracle.cu), which calls the same cuRAND header on
+the host.  Its `logf` is glibc's, so a sampled position may differ where the quotient sits
+within one ulp of an integer; the oracle counts such draws ("fragile") and the comparison
+allows that many rows to differ.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import brainpylib_b200 as bpl
+from brainpylib_b200 import gpu_ops, jitconn_ops
+from oracle import cpu, ref
+
+pytestmark = pytest.mark.gpu
+needs_ref_gpu = pytest.mark.skipif(not ref.available_gpu(), reason='oracle/_ref/libref_gpu.so not built')
+
+KINDS = [('homo', 0., 0.), ('uniform', -0.1, 0.2), ('normal', 0., 0.01)]
+ORACLE_KIND = {'homo': cpu.W_HOMO, 'uniform': cpu.W_UNIFORM, 'normal': cpu.W_NORMAL}
+
+
+def descriptor(kind, n_row, n_col, seed, conn_prob, w1, w2):
+  return jitconn_ops._descriptor(kind, n_row, n_col, seed, conn_prob, w1, w2)
+
+
+def call_event(events, kind, w1, w2, conn_prob, shape, seed, transpose, odp):
+  if kind == 'homo':
+    return bpl.event_matvec_prob_conn_homo_weight(events, 1., conn_prob=conn_prob, shape=shape, seed=seed,
+                                                  transpose=transpose, outdim_parallel=odp)
+  if kind == 'uniform':
+    return bpl.event_matvec_prob_conn_uniform_weight(events, w_low=w1, w_high=w1 + w2, conn_prob=conn_prob,
+                                                     shape=shape, seed=seed, transpose=transpose, outdim_parallel=odp)
+  return bpl.event_matvec_prob_conn_normal_weight(events, w_mu=w1, w_sigma=w2, conn_prob=conn_prob, shape=shape,
+                                                  seed=seed, transpose=transpose, outdim_parallel=odp)
+
+
+def call_dense(vector, kind, w1, w2, conn_prob, shape, seed, transpose, odp):
+  if kind == 'homo':
+    return bpl.matvec_prob_conn_homo_weight(vector, 1., conn_prob=conn_prob, shape=shape, seed=seed,
+                                            transpose=transpose, outdim_parallel=odp)
+  if kind == 'uniform':
+    return bpl.matvec_prob_conn_uniform_weight(vector, w_low=w1, w_high=w1 + w2, conn_prob=conn_prob, shape=shape,
+                                               seed=seed, transpose=transpose, outdim_parallel=odp)
+  return bpl.matvec_prob_conn_normal_weight(vector, w_mu=w1, w_sigma=w2, conn_prob=conn_prob, shape=shape,
+                                            seed=seed, transpose=transpose, outdim_parallel=odp)
+
+
+@needs_ref_gpu
+@pytest.mark.parametrize('kind,w1,w2', KINDS)
+@pytest.mark.parametrize('odp', [True, False])
+@pytest.mark.parametrize('ev_dtype', [torch.bool, torch.float32, torch.float64])
+def test_event_matvec_equals_reference_kernels(cuda, kind, w1, w2, odp, ev_dtype):
+  g = torch.Generator(device='cpu').manual_seed(5)
+  for shape, prob in [((100, 200), 0.1), ((10, 1000), 0.01), ((1000, 10), 0.4), ((2, 1000), 0.1), ((1000, 2), 0.5),
+                      ((5000, 6000), 0.02)]:
+    for transpose in (False, True):
+      n_in = shape[0] if transpose else shape[1]
+      n_out = shape[1] if transpose else shape[0]
+      ev = torch.rand(n_in, generator=g) < 0.2
+      if ev_dtype != torch.bool:
+        ev = ev.to(ev_dtype) * (torch.rand(n_in, generator=g).to(ev_dtype) + 0.5)   # values other than 1
+      ev = ev.to(cuda)
+      y = call_event(ev, kind, w1, w2, prob, shape, 1234, transpose, odp)
+      y_ref = torch.full_like(y, float('nan'))
+      tname = 'float' if y.dtype == torch.float32 else 'double'
+      ename = 'bool' if ev_dtype == torch.bool else tname
+      name = f'gpu_event_matvec{"" if odp else "_atomic"}_prob_{kind}_v2_{tname}_{ename}'
+      ref.gpu_call(name, [ev, y_ref], descriptor(kind, n_out, n_in, 1234, prob, w1, w2))
+      if odp or kind == 'homo':
+        assert torch.equal(y, y_ref), (shape, transpose, (y - y_ref).abs().max())
+      else:
+        torch.testing.assert_close(y, y_ref, rtol=1e-5, atol=1e-5 * max(1., prob * n_in))
+
+
+@needs_ref_gpu
+@pytest.mark.parametrize('kind,w1,w2', KINDS)
+@pytest.mark.parametrize('odp', [True, False])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+def test_matvec_equals_reference_kernels(cuda, kind, w1, w2, odp, dtype):
+  g = torch.Generator(device='cpu').manual_seed(6)
+  for shape, prob in [((100, 200), 0.1), ((10, 1000), 0.01), ((1000, 10), 0.4), ((3000, 2500), 0.05)]:
+    for transpose in (False, True):
+      n_in = shape[0] if transpose else shape[1]
+      n_out = shape[1] if transpose else shape[0]
+      v = torch.randn(n_in, generator=g, dtype=dtype).to(cuda)
+      y = call_dense(v, kind, w1, w2, prob, shape, 99, transpose, odp)
+      y_ref = torch.full_like(y, float('nan'))
+      tname = 'float' if dtype == torch.float32 else 'double'
+      name = f'gpu_matvec{"" if odp else "_atomic"}_prob_{kind}_v2_{tname}'
+      ref.gpu_call(name, [v, y_ref], descriptor(kind, n_out, n_in, 99, prob, w1, w2))
+      if odp:
+        assert torch.equal(y, y_ref), (shape, transpose, (y - y_ref).abs().max())
+      else:
+        torch.testing.assert_close(y, y_ref, rtol=1e-5 if dtype == torch.float32 else 1e-12,
+                                   atol=1e-5 * max(1., prob * n_in) * (1. if kind == 'homo' else 0.2))
+
+
+@needs_ref_gpu
+def test_mask_kernel_path_equals_reference(cuda):
+  """Large enough for the shared-memory bitmask kernel (>= 4096 rows), bool and float events."""
+  shape, prob = (20000, 30000), 0.01
+  g = torch.Generator(device='cpu').manual_seed(7)
+  ev = (torch.rand(shape[1], generator=g) < 0.05).to(cuda)
+  for kind, w1, w2 in KINDS:
+    for e in (ev, ev.float() * 2.5):
+      y = call_event(e, kind, w1, w2, prob, shape, 42, False, True)
+      y_ref = torch.empty_like(y)
+      ename = 'bool' if e.dtype == torch.bool else 'float'
+      ref.gpu_call(f'gpu_event_matvec_prob_{kind}_v2_float_{ename}', [e, y_ref],
+                   descriptor(kind, shape[0], shape[1], 42, prob, w1, w2))
+      assert torch.equal(y, y_ref), kind
+
+
+@pytest.mark.parametrize('kind,w1,w2', KINDS)
+def test_against_cpu_oracle(cuda, kind, w1, w2):
+  shape, prob, seed = (2000, 3000), 0.05, 4321
+  rng = np.random.default_rng(8)
+  ev = rng.random(shape[1]) < 0.1
+  y = call_event(torch.as_tensor(ev).to(cuda), kind, w1, w2, prob, shape, seed, False, True).cpu().numpy()
+  want, info = cpu.jitconn_event_matvec(ev, kind=ORACLE_KIND[kind], w1=w1, w2=w2, conn_prob=prob, shape=shape,
+                                        seed=seed, return_info=True)
+  assert 0.8 < info['connections'] / (prob * shape[0] * shape[1]) < 1.2
+  tol = dict(rtol=1e-5, atol=1e-6) if kind != 'normal' else dict(rtol=1e-4, atol=1e-5)   # host sinf/cosf vs device
+  bad = ~np.isclose(y, want, **tol)
+  assert bad.sum() <= info['fragile'], (bad.sum(), info)
+  # dense vector, both orientations
+  x = rng.standard_normal(shape[1]).astype(np.float32)
+  for odp in (True, False):
+    y = call_dense(torch.as_tensor(x).to(cuda), kind, w1, w2, prob, shape, seed, False, odp).cpu().numpy()
+    want, info = cpu.jitconn_matvec(x, kind=ORACLE_KIND[kind], w1=w1, w2=w2, conn_prob=prob, shape=shape, seed=seed,
+                                    outdim_parallel=odp, return_info=True)
+    bad = ~np.isclose(y, want, rtol=1e-4, atol=1e-3 if kind == 'homo' else 1e-4)
+    assert bad.sum() <= 4 * info['fragile'] + (0 if odp else 0), (odp, bad.sum(), info)
+
+
+def test_relations_of_the_reference_tests(cuda):
+  """brainpylib/_src/jitconn_ops/tests/test_event_matvec.py:63-87 and test_matvec.py:55-81."""
+  g = torch.Generator(device='cpu').manual_seed(9)
+  for shape in cases.JITCONN_SHAPES:
+    for prob in (0.01, 0.1, 0.5):
+      for kind, w1, w2 in KINDS:
+        for transpose in (False, True):
+          for odp in (True, False):
+            n_in = shape[0] if transpose else shape[1]
+            ev = (torch.rand(n_in, generator=g) < 0.1).to(cuda)
+            r1 = call_event(ev, kind, w1, w2, prob, shape, 1234, transpose, odp)
+            r2 = call_event(ev, kind, w1, w2, prob, shape, 1234, transpose, odp)
+            if odp or kind == 'homo':
+              assert torch.equal(r1, r2)
+            else:
+              torch.testing.assert_close(r1, r2, rtol=1e-5, atol=1e-6)
+            r3 = call_event(ev, kind, w1, w2, prob, shape[::-1], 1234, not transpose, odp)
+            torch.testing.assert_close(r1, r3, rtol=1e-5, atol=1e-6)
+            # bool events == float 0/1 events
+            r4 = call_event(ev.float(), kind, w1, w2, prob, shape, 1234, transpose, odp)
+            torch.testing.assert_close(r1, r4, rtol=1e-5, atol=1e-6)
+            # dense product on the 0/1 vector
+            r5 = call_dense(ev.float(), kind, w1, w2, prob, shape, 1234, transpose, odp)
+            torch.testing.assert_close(r1, r5, rtol=1e-5, atol=1e-6)
+
+
+def test_row_and_column_parallel_are_transposes(cuda):
+  """(shape, T, odp) and (shape, not T, not odp) walk the same streams: <M x, z> == <x, M^T z>, and
+  the autograd rule (brainpylib/_src/jitconn_ops/matvec.py:393-402) relies on it."""
+  shape, prob, seed = (700, 900), 0.05, 77
+  g = torch.Generator(device='cpu').manual_seed(10)
+  for kind, w1, w2 in KINDS:
+    x = torch.randn(shape[1], generator=g, dtype=torch.float64).to(cuda)
+    z = torch.randn(shape[0], generator=g, dtype=torch.float64).to(cuda)
+    mx = call_dense(x, kind, w1, w2, prob, shape, seed, False, True)
+    mtz = call_dense(z, kind, w1, w2, prob, shape, seed, True, False)
+    torch.testing.assert_close(torch.dot(mx, z), torch.dot(x, mtz), rtol=1e-9, atol=1e-9)
+    xg = x.clone().requires_grad_(True)
+    y = call_dense(xg, kind, w1, w2, prob, shape, seed, False, True)
+    gx, = torch.autograd.grad(y, xg, z)
+    torch.testing.assert_close(gx, mtz, rtol=1e-12, atol=1e-12)
+    eg = (torch.rand(shape[1], generator=g) < 0.3).double().to(cuda).requires_grad_(True)
+    ye = call_event(eg, kind, w1, w2, prob, shape, seed, False, True)
+    ge, = torch.autograd.grad(ye, eg, z)
+    torch.testing.assert_close(ge, mtz, rtol=1e-12, atol=1e-12)
+
+
+def test_edge_parameters(cuda):
+  """conn_prob 1e-4, 0.5 and 1.0; a single input; seeds next to 2^32 (seed + row wraps)."""
+  ev = torch.ones(300, dtype=torch.bool, device=cuda)
+  y = bpl.event_matvec_prob_conn_homo_weight(ev, 1., conn_prob=1.0, shape=(50, 300), seed=3)
+  # every gap is 1 when conn_prob >= 1: positions 1..299 connect, position 0 does not
+  assert torch.equal(y, torch.full((50,), 299., device=cuda))
+  y = bpl.event_matvec_prob_conn_homo_weight(ev, 1., conn_prob=1e-4, shape=(50, 300), seed=3)
+  assert y.sum().item() <= 50
+  y1 = bpl.event_matvec_prob_conn_homo_weight(ev[:1], 1., conn_prob=0.5, shape=(50, 1), seed=3)
+  assert y1.shape == (50,) and y1.max().item() <= 1
+  for seed in (2 ** 32 - 3, 2 ** 32 - 1):
+    a = bpl.event_matvec_prob_conn_homo_weight(ev, 1., conn_prob=0.1, shape=(50, 300), seed=seed)
+    want = cpu.jitconn_event_matvec(np.ones(300, np.bool_), kind=cpu.W_HOMO, conn_prob=0.1, shape=(50, 300), seed=seed)
+    assert (a.cpu().numpy() != want).sum() <= 1
+    # rows 3.. of the wrapped seed are rows 0.. of seed 0
+    if seed == 2 ** 32 - 3:
+      b = bpl.event_matvec_prob_conn_homo_weight(ev, 1., conn_prob=0.1, shape=(47, 300), seed=0)
+      assert torch.equal(a[3:], b)
+
+
+@needs_ref_gpu
+@pytest.mark.parametrize('kind,w1,w2', KINDS[1:])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+def test_matmat_equals_reference_kernels(cuda, kind, w1, w2, dtype):
+  g = torch.Generator(device='cpu').manual_seed(11)
+  for m in (5, 8, 15, 33, 64):
+    for shape, prob in [((100, 200), 0.1), ((10, 1000), 0.05), ((1000, 10), 0.2), ((200, 200), 0.01),
+                        ((1500, 700), 0.02)]:
+      # the reference reads X out of bounds for row groups that are not full (lib/gpu_jitconn_matmat.cu:265);
+      # give it a padded copy so that the stray reads stay inside the allocation
+      X = torch.randn(m, shape[0], generator=g, dtype=dtype).to(cuda)
+      pad = torch.zeros(((m + 31) // 32 * 32 + 32) * shape[0], dtype=dtype, device=cuda)
+      pad[: m * shape[0]] = X.reshape(-1)
+      if kind == 'uniform':
+        Y = bpl.matmat_prob_conn_uniform_weight(X, w_low=w1, w_high=w1 + w2, conn_prob=prob, shape=shape, seed=7)
+      else:
+        Y = bpl.matmat_prob_conn_normal_weight(X, w_mu=w1, w_sigma=w2, conn_prob=prob, shape=shape, seed=7)
+      Y_ref = torch.empty_like(Y)
+      tname = 'float' if dtype == torch.float32 else 'double'
+      opaque = gpu_ops.build_matmat_jit_prob_descriptor1(m, shape[0], shape[1], 7, jitconn_ops._log_p(prob), w1, w2)
+      ref.gpu_call(f'gpu_matmat_prob_prob_{kind}_{tname}_v1', [pad, Y_ref], opaque)
+      assert torch.equal(Y, Y_ref), (m, shape, (Y - Y_ref).abs().max())
+
+
+def test_matmat_equals_matvec_per_row(cuda):
+  """brainpylib/_src/jitconn_ops/tests/matmat_testcase.py:59-78,119-138."""
+  g = torch.Generator(device='cpu').manual_seed(12)
+  for m in (5, 33):
+    for shape in cases.MATMAT_SHAPES:
+      for prob in (0.01, 0.2):
+        X = torch.randn(m, shape[0], generator=g).to(cuda)
+        Y = bpl.matmat_prob_conn_normal_weight(X, w_mu=0., w_sigma=0.01, conn_prob=prob, shape=shape, seed=1234)
+        Y2 = bpl.matmat_prob_conn_normal_weight(X, w_mu=0., w_sigma=0.01, conn_prob=prob, shape=shape, seed=1234)
+        assert torch.equal(Y, Y2)
+        rows = torch.stack([bpl.matvec_prob_conn_normal_weight(X[r], w_mu=0., w_sigma=0.01, conn_prob=prob,
+                                                               shape=shape, seed=1234, transpose=True)
+                            for r in range(m)])
+        assert torch.equal(Y, rows)
+        U = bpl.matmat_prob_conn_uniform_weight(X, w_low=-0.1, w_high=0.1, conn_prob=prob, shape=shape, seed=1234)
+        rows = torch.stack([bpl.matvec_prob_conn_uniform_weight(X[r], w_low=-0.1, w_high=0.1, conn_prob=prob,
+                                                                shape=shape, seed=1234, transpose=True)
+                            for r in range(m)])
+        assert torch.equal(U, rows)
+
+
+def test_matmat_against_cpu_oracle(cuda):
+  rng = np.random.default_rng(13)
+  X = rng.standard_normal((16, 3000)).astype(np.float32)
+  Y = bpl.matmat_prob_conn_uniform_weight(torch.as_tensor(X).to(cuda), w_low=-0.1, w_high=0.1, conn_prob=0.02,
+                                          shape=(3000, 500), seed=7).cpu().numpy()
+  want, info = cpu.jitconn_matmat(X, kind=cpu.W_UNIFORM, w1=-0.1, w2=0.2, conn_prob=0.02, shape=(3000, 500), seed=7,
+                                  return_info=True)
+  bad_cols = (~np.isclose(Y, want, rtol=1e-5, atol=1e-6)).any(axis=0)
+  assert bad_cols.sum() <= info['fragile'], (bad_cols.sum(), info)

@@ -346,7 +346,8 @@ row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restri
         }
         if (EVENT && HOMO) {
             hits = group_sum(hits, static_cast<int>(lpr));
-            acc = static_cast<T>(static_cast<double>(hits) * static_cast<double>(homo_w));
+            // no hit leaves +0 like an empty sum (the product with a negative weight would give -0)
+            acc = hits ? static_cast<T>(static_cast<double>(hits) * static_cast<double>(homo_w)) : T(0);
         } else {
             acc = group_sum(acc, static_cast<int>(lpr));
         }

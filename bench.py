@@ -118,7 +118,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # workload
 # ------------------------------------------------------------------------------------------------
-def build_workload(n_steps, keep_host_matrix, device=None, shard=None):
+def build_workload(n_steps, keep_host_matrix, device=None, shard=None, n_neurons=N_NEURONS):
   """The matrix on `device` (or only on the host) plus `n_steps` spike vectors (host, float32).
 
   `shard` = (rank, world): keep only the synapses whose target lies in this rank's contiguous
@@ -133,11 +133,11 @@ def build_workload(n_steps, keep_host_matrix, device=None, shard=None):
   lo = hi = None
   if shard is not None:
     rank, world = shard
-    per = (N_NEURONS + world - 1) // world
-    lo, hi = rank * per, min(N_NEURONS, (rank + 1) * per)
+    per = (n_neurons + world - 1) // world
+    lo, hi = rank * per, min(n_neurons, (rank + 1) * per)
   masks = []
   rng = None
-  for kind, c, arr in workloads.c3_matrix_chunks(N_NEURONS):
+  for kind, c, arr in workloads.c3_matrix_chunks(n_neurons):
     if kind == 'rng':
       rng = arr
       continue
@@ -155,7 +155,7 @@ def build_workload(n_steps, keep_host_matrix, device=None, shard=None):
           t = t[masks[c]]
           masks[c] = None
       dev[kind].append(t)
-  events = [workloads.c3_events(rng, N_NEURONS, RATE) for _ in range(n_steps)]
+  events = [workloads.c3_events(rng, n_neurons, RATE) for _ in range(n_steps)]
   out = {'events': events, 'gen_seconds': None}
   if device is not None:
     out['indices'] = torch.cat(dev['indices'])
@@ -163,19 +163,24 @@ def build_workload(n_steps, keep_host_matrix, device=None, shard=None):
     out['data'] = torch.cat(dev['data'])
     dev['data'] = None
     if shard is None:
-      out['indptr'] = torch.arange(0, N_NEURONS * DEGREE + 1, DEGREE, dtype=torch.int32, device=device)
-      out['shape'] = (N_NEURONS, N_NEURONS)
+      out['indptr'] = torch.arange(0, n_neurons * DEGREE + 1, DEGREE, dtype=torch.int32, device=device)
+      out['shape'] = (n_neurons, n_neurons)
     else:
-      ptr = torch.zeros(N_NEURONS + 1, dtype=torch.int64, device=device)
+      ptr = torch.zeros(n_neurons + 1, dtype=torch.int64, device=device)
       ptr[1:] = torch.cumsum(torch.cat(lengths).to(torch.int64), 0)
       out['indptr'] = ptr.to(torch.int32)
-      out['shape'] = (N_NEURONS, hi - lo)
+      out['shape'] = (n_neurons, hi - lo)
     torch.cuda.synchronize()
   if keep_host_matrix:
     out['host_indices'], out['host_data'] = host['indices'][0], host['data'][0]
     out['host_indptr'] = np.arange(0, CPU_SAMPLE_ROWS * DEGREE + 1, DEGREE, dtype=np.int32)
   out['gen_seconds'] = time.time() - t0
   return out
+
+
+def workloads_chunk_rows():
+  from brainpylib_b200 import workloads
+  return workloads.C3_ROWS_PER_CHUNK
 
 
 def cpu_reference_kernel():
@@ -267,7 +272,12 @@ def run_ours(args):
   K, W = args.steps, args.warmup
   total = W + K
   want_cpu = (world == 1 and rank == 0 and not args.no_cpu_baseline)
-  work = build_workload(total, keep_host_matrix=want_cpu, device=device, shard=(rank, world) if world > 1 else None)
+  n_neurons = args.neurons
+  if n_neurons % workloads_chunk_rows() != 0 or n_neurons % world != 0:
+    raise SystemExit('--neurons must be a multiple of 100000 and of the number of ranks')
+  want_cpu = want_cpu and n_neurons == N_NEURONS
+  work = build_workload(total, keep_host_matrix=want_cpu, device=device, shard=(rank, world) if world > 1 else None,
+                        n_neurons=n_neurons)
   log(f'[bench] rank {rank}: workload built in {work["gen_seconds"]:.1f}s, '
       f'{work["indices"].numel():,} synapses on device')
   shape = work['shape']
@@ -281,8 +291,8 @@ def run_ours(args):
 
   # N > 1: every rank produces the spikes of its own 1/N of the neurons and the dense spike vector is
   # all-gathered (NCCL over NVLink) inside the step; the matrix shard then needs no further exchange.
-  per = N_NEURONS // world
-  ev_full = torch.empty(N_NEURONS, dtype=torch.float32, device=device) if world > 1 else None
+  per = n_neurons // world
+  ev_full = torch.empty(n_neurons, dtype=torch.float32, device=device) if world > 1 else None
 
   def step(s, out=y):
     events = ev_dev[s]
@@ -369,12 +379,12 @@ def run_ours(args):
 
   peak, peak_src = measured_peaks()
   n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
-  s_local = float(work['indices'].numel()) / (N_NEURONS * DEGREE) * n_act * DEGREE   # this rank's synapses per step
+  s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
   # algorithmic bytes of one scatter launch: indices + weights of the active rows (8 B per synapse),
   # their indptr pairs (8 B per active row) and the write-back of y (4 B per output neuron)
   k_bytes = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
   # whole step: + the spike scan (4 B per pre neuron) and the zero-fill of y (4 B per output neuron)
-  step_bytes = k_bytes + 4.0 * N_NEURONS + 4.0 * shape[1]
+  step_bytes = k_bytes + 4.0 * n_neurons + 4.0 * shape[1]
   achieved = k_bytes / (k_ms * 1e-3) / 1e9
   roofline = {
     'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec>', 'achieved': achieved, 'peak': peak,
@@ -388,7 +398,9 @@ def run_ours(args):
     'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': K, 'warmup': W,
     'ms_per_step': ms / K, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
     'data': 'synthetic',
-    'config': {'workload': WORKLOAD, 'l2': 'inputs larger than L2: each step streams a different ~80 MB of the '
+    'config': {'workload': WORKLOAD if n_neurons == N_NEURONS else
+               f'REDUCED TWIN of C3 for profiler captures: {n_neurons} neurons x 1000 synapses (not the benchmark size)',
+               'l2': 'inputs larger than L2: each step streams a different ~80 MB of the '
                '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
                'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
                'ranks; each rank owns 1/N of the spike sources; NCCL all-gather of the dense spike vector '
@@ -467,6 +479,8 @@ def main():
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--neurons', type=int, default=N_NEURONS,
+                  help='reduced twin of the workload (multiple of 100000), for profiler captures only')
   args = ap.parse_args()
   if args.warmup < 3 and args.impl == 'ours':
     log('[bench] note: fewer than 3 warm-up steps requested; the timing rules ask for >= 3')

@@ -513,3 +513,106 @@ CSR_TARGET(csr_matvec_transpose_heter_float, float, false, true, 3)
 CSR_TARGET(csr_matvec_transpose_heter_double, double, false, true, 3)
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Transposed event product that allocates nothing and takes no workspace buffer
+// ------------------------------------------------------------------------------------------
+// Who needs it: a caller that runs as an XLA custom call (or inside any framework's stream
+// capture) receives exactly the buffers the framework planned for it and must not call
+// cudaMalloc itself: allocation is illegal while a stream is being captured, synchronises
+// the device, and takes memory behind the back of the framework's own allocator.  The
+// regular targets solve this by asking for one extra workspace buffer; a caller that cannot
+// even declare that extra buffer (it must keep the reference's exact five-buffer list) can
+// use this entry point instead.  Its scratch (the compacted spike list) lives in a
+// file-scope device array of fixed size, so the number of matrix rows is limited.
+//
+// Cost and rules of the fixed array:
+//  * every GPU that loads this library holds BPL_NOALLOC_MAX_ROWS * 4 + 4096 bytes (about
+//    8.4 MB) from the first use of the library on that GPU until the process exits;
+//  * all calls on one GPU share it.  Nothing in it has to start at zero (every word that is
+//    read was written earlier in the same call), so stale contents of an earlier call are
+//    harmless, but two calls that overlap on the GPU (different streams, no ordering between
+//    them) race on it and give wrong results: keep such calls on one stream or order them;
+//  * the first call on a device looks the array's device address up (cudaGetSymbolAddress,
+//    with that device current).  That one call should be made before any stream capture
+//    begins; later calls only launch kernels.
+constexpr uint32_t NOALLOC_MAX_ROWS = 1u << 21;   // 2,097,152 rows
+static __device__ __align__(256) uint32_t g_noalloc_scratch[MAX_CHUNKS + NOALLOC_MAX_ROWS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+uint32_t *g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch array on the current device.  In host code the array's name
+// is only a handle for the runtime, not a pointer a kernel could use.
+uint32_t *noalloc_scratch_address() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        set_status(BPL_ERR_CUDA, "no-allocation entry point: cannot identify the current device");
+        return nullptr;
+    }
+    uint32_t *p = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_ACQUIRE);
+    if (p != nullptr) return p;
+    void *addr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
+    if (e != cudaSuccess || addr == nullptr) {
+        set_status(BPL_ERR_CUDA, e != cudaSuccess ? cudaGetErrorString(e) : "cudaGetSymbolAddress returned null");
+        return nullptr;
+    }
+    // a racing first call on another host thread stores the same address
+    __atomic_store_n(&g_noalloc_ptr[dev], static_cast<uint32_t *>(addr), __ATOMIC_RELEASE);
+    return static_cast<uint32_t *>(addr);
+}
+}  // namespace
+
+extern "C" {
+
+uint32_t bpl_noalloc_max_rows(void) { return NOALLOC_MAX_ROWS; }
+
+// y = A^T events for heterogeneous float32 weights and float32 events, transpose only.
+// buffers: [data f32(nse), indices u32(nse), indptr u32(n_row+1), events f32(n_row), y f32(n_col)]
+// opaque : TwoUintOneBoolDescriptor{n_row, n_col, transpose = true}
+void event_csr_matvec_heter_float_float_noalloc(bpl_stream_t stream, void **buffers, const char *opaque,
+                                                size_t opaque_len) {
+    const TwoUintOneBoolDescriptor *d = unpack<TwoUintOneBoolDescriptor>(opaque, opaque_len);
+    if (!d) return;
+    if (!d->bool_x) {
+        set_status(BPL_ERR_ARGUMENT, "the no-allocation entry point computes transpose=True only");
+        return;
+    }
+    const uint32_t n_row = d->uint_x, n_col = d->uint_y;
+    if (n_row > NOALLOC_MAX_ROWS) {
+        set_status(BPL_ERR_TOO_LARGE,
+                   "event_csr_matvec_heter_float_float_noalloc: more than 2097152 matrix rows; "
+                   "use event_csr_matvec_heter_float_float with a workspace buffer");
+        return;
+    }
+    if (n_col == 0) return;
+    uint32_t *scratch = noalloc_scratch_address();
+    if (scratch == nullptr) return;
+    const float *data = static_cast<const float *>(buffers[0]);
+    const uint32_t *indices = static_cast<const uint32_t *>(buffers[1]);
+    const uint32_t *indptr = static_cast<const uint32_t *>(buffers[2]);
+    const float *events = static_cast<const float *>(buffers[3]);
+    float *y = static_cast<float *>(buffers[4]);
+    uint32_t *counts = scratch, *ids = scratch + MAX_CHUNKS;
+
+    const ScanPlan p = plan_scan(n_row);
+    const uint64_t zero_blocks = (static_cast<uint64_t>(n_col) + SCAN_TILE - 1) / SCAN_TILE;
+    const uint64_t zero_cap = static_cast<uint64_t>(sm_count()) * 8;
+    const uint32_t scan_grid = static_cast<uint32_t>(
+        max(static_cast<uint64_t>(p.n_chunks), min(zero_blocks, zero_cap)));
+    scan_events_kernel<float, float><<<scan_grid, SCAN_THREADS, 0, stream>>>(
+        events, n_row, p.chunk, p.n_chunks, y, n_col, counts, ids);
+    if (!launch_ok() || n_row == 0) return;
+    const int grid = persistent_blocks(4, static_cast<uint64_t>(n_row) * 16);
+    if (aligned16(indices) && aligned16(data))
+        row_scatter_kernel<float, false, true, true><<<grid, ROW_THREADS, 0, stream>>>(
+            indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
+    else
+        row_scatter_kernel<float, false, true, false><<<grid, ROW_THREADS, 0, stream>>>(
+            indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
+    launch_ok();
+}
+
+}  // extern "C"

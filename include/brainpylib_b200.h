@@ -177,6 +177,20 @@ void bpl_profile_scatter_events(void *before, void *after);
 BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
 #undef BPL_DECLARE_ONE
 
+/* ---- transposed event product without workspace and without allocation ------------------
+ * No counterpart in the reference.  Same computation as event_csr_matvec_heter_float_float
+ * with transpose=true, for callers that may neither allocate device memory nor pass the extra
+ * workspace buffer (an XLA custom call that must keep the reference's exact buffer list, code
+ * running under stream capture): the scratch is a fixed device array inside the library.
+ *   buffers [data f32(nse), indices u32(nse), indptr u32(n_row+1), events f32(n_row), y f32(n_col)]
+ *   opaque  TwoUintOneBoolDescriptor{n_row, n_col, transpose=true}
+ * Limits: n_row <= bpl_noalloc_max_rows() (2,097,152), else status BPL_ERR_TOO_LARGE and nothing
+ * runs; about 8.4 MB of device memory per GPU for the life of the process; calls that overlap on
+ * one GPU race on the shared scratch (serialise them); the first call on a device resolves the
+ * scratch address and should precede any stream capture. */
+uint32_t bpl_noalloc_max_rows(void);
+BPL_DECLARE_TARGET(event_csr_matvec_heter_float_float_noalloc);
+
 #ifdef __cplusplus
 }
 #endif

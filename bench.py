@@ -421,7 +421,21 @@ def run_ours(args):
   if rank == 0:
     print(json.dumps(line), flush=True)
   if world > 1:
+    # Tear down in a fixed order: the captured graphs hold NCCL kernels and must go before the
+    # communicator.  A process that still cannot finish the teardown within 30 s leaves anyway:
+    # the measurement is complete and printed, and a launcher must not wait on it for ever.
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph.reset()
+    warm.reset()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    watchdog = threading.Timer(30.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
     dist.destroy_process_group()
+    watchdog.cancel()
 
 
 def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
@@ -479,11 +493,17 @@ def main():
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
+                  help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
+                       '(1 GPU, see brainpylib_b200/config_bench.py)')
   ap.add_argument('--neurons', type=int, default=N_NEURONS,
                   help='reduced twin of the workload (multiple of 100000), for profiler captures only')
   args = ap.parse_args()
   if args.warmup < 3 and args.impl == 'ours':
     log('[bench] note: fewer than 3 warm-up steps requested; the timing rules ask for >= 3')
+  if args.config != 'c3':
+    from brainpylib_b200 import config_bench
+    return config_bench.main([args.config, '--warmup', str(args.warmup)])
   if args.impl == 'reference':
     run_reference(args)
   else:

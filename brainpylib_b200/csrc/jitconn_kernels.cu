@@ -26,16 +26,106 @@ enum { W_HOMO = 0, W_UNIFORM = 1, W_NORMAL = 2 };
 struct Stream {
     curandState st;
     double log_p;
+    float inv_log_p;   // float(1 / log_p)
+    float tol_k;       // |inv_log_p| * 2^-20; negative when the shortcuts are switched off
 
     __device__ __forceinline__ Stream(unsigned int stream_seed, double lp) : log_p(lp) {
         curand_init(stream_seed, 0, 0, &st);
+        inv_log_p = (float) (1.0 / lp);
+        // log(u) lies in [-22.9, 0]; the shortcuts need 0 <= q = log(u) / log_p < 2^20
+        const bool ok = inv_log_p < 0.0f && inv_log_p > -45000.0f;
+        tol_k = ok ? -inv_log_p * 9.5367432e-7f : -1.0f;
     }
-    __device__ __forceinline__ int gap() { return (int) ceil(log(curand_uniform(&st)) / log_p); }
-    __device__ __forceinline__ unsigned int ugap() { return (unsigned int) ceil(log(curand_uniform(&st)) / log_p); }
+
+    // The reference's gap is (int) ceil(log(u) / log_p): float log, double division, ceil.
+    // It is reproduced exactly in up to three stages, each falling through to the next when it
+    // cannot prove the result:
+    //  (1) q = __logf(u) * float(1 / log_p).  __logf is within 2^-21.41 (absolute, u in [0.5, 2])
+    //      or 3 ulp of the true logarithm and logf within 1 ulp; with the float rounding of the
+    //      product (2^-23 q) q is within |1 / log_p| * max(2^-21.19 + 2^-23 |log u|, 1.25 * 2^-21 |log u|)
+    //      of the reference's quotient.  The test distance |1 / log_p| * 2^-20 * (1 + 1.5 |log u|) is
+    //      more than 2.2x that bound everywhere, so when q is farther than it from the nearest
+    //      integer the reference's quotient lies strictly between the same two integers: same ceil.
+    //  (2) the same test with the accurate logf (the value the reference uses): error < 2^-22.9 q,
+    //      margin 2^-21 q.
+    //  (3) the reference's own expression.
+    // rint(q) and its integer value come from adding 1.5 * 2^23, exact for 0 <= q < 2^22.
+    // At a mean gap of 1000 about 1 draw in 200 leaves stage 1 and 1 in 1000 stage 2.
+    __device__ __forceinline__ int gap() {
+        const float u = curand_uniform(&st);
+        if (tol_k > 0.0f) {
+            const float a = __logf(u);
+            const float q = a * inv_log_p;
+            const float t = q + 12582912.0f;
+            const float frac = q - (t - 12582912.0f);
+            if (fabsf(frac) > fmaf(fabsf(a), 1.5f * tol_k, tol_k))
+                return (__float_as_int(t) - 0x4B400000) + (frac > 0.0f ? 1 : 0);
+            const float lg = log(u);
+            const float q2 = lg * inv_log_p;
+            const float t2 = q2 + 12582912.0f;
+            const float frac2 = q2 - (t2 - 12582912.0f);
+            if (fabsf(frac2) > q2 * 4.8e-7f)
+                return (__float_as_int(t2) - 0x4B400000) + (frac2 > 0.0f ? 1 : 0);
+            return (int) ceil(lg / log_p);
+        }
+        return (int) ceil(log(u) / log_p);
+    }
+    // the matmat kernels of the reference hold positions as `unsigned int` (lib/gpu_jitconn_matmat.cu:252);
+    // the shortcuts only return non-negative values, for which both conversions agree
+    __device__ __forceinline__ unsigned int ugap() {
+        const float u = curand_uniform(&st);
+        if (tol_k > 0.0f) {
+            const float a = __logf(u);
+            const float q = a * inv_log_p;
+            const float t = q + 12582912.0f;
+            const float frac = q - (t - 12582912.0f);
+            if (fabsf(frac) > fmaf(fabsf(a), 1.5f * tol_k, tol_k))
+                return (unsigned int) ((__float_as_int(t) - 0x4B400000) + (frac > 0.0f ? 1 : 0));
+            const float lg = log(u);
+            const float q2 = lg * inv_log_p;
+            const float t2 = q2 + 12582912.0f;
+            const float frac2 = q2 - (t2 - 12582912.0f);
+            if (fabsf(frac2) > q2 * 4.8e-7f)
+                return (unsigned int) ((__float_as_int(t2) - 0x4B400000) + (frac2 > 0.0f ? 1 : 0));
+            return (unsigned int) ceil(lg / log_p);
+        }
+        return (unsigned int) ceil(log(u) / log_p);
+    }
     template<typename T, int KIND>
     __device__ __forceinline__ T weight(double w1, double w2) {
         if (KIND == W_UNIFORM) return (T) (curand_uniform(&st) * w2 + w1);
         if (KIND == W_NORMAL) return (T) (curand_normal(&st) * w2 + w1);
+        return T(1);
+    }
+};
+
+// A synapse weight whose raw draws are taken immediately (the stream must advance exactly as in
+// the reference) but whose value is only computed when asked for.  Event products ask for it on
+// a hit only, which skips the conversions, the double multiply-add and (normal) the Box-Muller
+// transform for every silent input.  The value is produced by cuRAND's own conversion functions
+// on the same raw draws, in the same pairing as curand_normal (two draws on odd calls, the
+// second half of the pair on even calls), so it is bit-identical.
+template<typename T, int KIND>
+struct LazyWeight {
+    unsigned int x, y;
+    int second;   // normal: 1 when the current value is the second half of the pair
+    int have;     // normal: 1 when an unused second half is pending
+
+    __device__ __forceinline__ LazyWeight() : x(0), y(0), second(0), have(0) {}
+    __device__ __forceinline__ void draw(curandState *st) {
+        if (KIND == W_UNIFORM) {
+            x = curand(st);
+        } else if (KIND == W_NORMAL) {
+            if (!have) { x = curand(st); y = curand(st); have = 1; second = 0; }
+            else { have = 0; second = 1; }
+        }
+    }
+    __device__ __forceinline__ T value(double w1, double w2) const {
+        if (KIND == W_UNIFORM) return (T) (_curand_uniform(x) * w2 + w1);
+        if (KIND == W_NORMAL) {
+            const float2 v = _curand_box_muller(x, y);
+            return (T) ((second ? v.y : v.x) * w2 + w1);
+        }
         return T(1);
     }
 };
@@ -79,14 +169,15 @@ jit_rows_event_kernel(const E *__restrict__ events, const unsigned int seed, con
     const unsigned int row_i = blockIdx.x * blockDim.x + threadIdx.x;
     if (row_i >= num_row) return;
     Stream s(seed + row_i, log_p);
+    LazyWeight<T, KIND> lw;
     T sum = 0;
     int pos = s.gap();
     while (pos < num_col) {
         if (KIND == W_HOMO) {
             sum += events[pos];
         } else {
-            const T rand = s.template weight<T, KIND>(w1, w2);
-            if (events[pos]) sum += rand;
+            lw.draw(&s.st);
+            if (events[pos]) sum += lw.value(w1, w2);
         }
         pos += s.gap();
     }
@@ -127,18 +218,21 @@ jit_rows_event_mask_kernel(const E *__restrict__ events, const unsigned int seed
     for (unsigned int row_i = blockIdx.x * MASK_THREADS + threadIdx.x; row_i < num_row;
          row_i += gridDim.x * MASK_THREADS) {
         Stream s(seed + row_i, log_p);
+        LazyWeight<T, KIND> lw;
         T sum = 0;
+        unsigned int hits = 0;   // homogeneous: events are 0 or 1, their float sum is the exact count (< 2^24)
         int pos = s.gap();
         while (pos < num_col) {
-            const bool hit = (mask[pos >> 5] >> (pos & 31)) & 1u;
+            const unsigned int hit = (mask[pos >> 5] >> (pos & 31)) & 1u;
             if (KIND == W_HOMO) {
-                sum += (T) hit;   // bool event value: 0 or 1
+                hits += hit;
             } else {
-                const T rand = s.template weight<T, KIND>(w1, w2);
-                if (hit) sum += rand;
+                lw.draw(&s.st);
+                if (hit) sum += lw.value(w1, w2);
             }
             pos += s.gap();
         }
+        if (KIND == W_HOMO) sum = (T) hits;
         out[row_i] = sum;
     }
 }
@@ -239,12 +333,9 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
     const unsigned int m_i = blockIdx.y * MM_ROWS;
     const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-    curandState st;
-    unsigned int pos = 0xffffffffu;
-    if (live) {
-        curand_init(seed + n_i, 0, 0, &st);
-        pos = (unsigned int) ceil(log(curand_uniform(&st)) / log_p);
-    }
+    Stream s(seed + n_i, log_p);
+    curandState &st = s.st;
+    unsigned int pos = live ? s.ugap() : 0xffffffffu;
     T sum[MM_ROWS];
 #pragma unroll
     for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
@@ -283,7 +374,7 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
                     sum[c * 2 + 1] += (x.y * rand);
                 }
             }
-            pos += (unsigned int) ceil(log(curand_uniform(&st)) / log_p);
+            pos += s.ugap();
         }
         __syncthreads();
     }

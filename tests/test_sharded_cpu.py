@@ -1,0 +1,104 @@
+"""World-size-2 checks of the multi-GPU sharding logic on CPU ranks (gloo): the column shards
+tile the matrix exactly, and all-gather + local product on each shard reproduces the oracle's
+result for the whole matrix.  The local product is the CPU oracle here (the CUDA operator is
+exercised by the GPU tests); what is under test is the partition and the exchange."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import cases
+from brainpylib_b200 import sharded
+from oracle import cpu
+
+
+def _free_port():
+  with socket.socket() as s:
+    s.bind(('127.0.0.1', 0))
+    return s.getsockname()[1]
+
+
+def _oracle_op(data, indices, indptr, events, *, shape, transpose):
+  y = cpu.event_csr_matvec(data.numpy(), indices.numpy(), indptr.numpy(), events.numpy(), shape=shape,
+                           transpose=transpose)
+  return torch.from_numpy(y)
+
+
+def _case(homo=False):
+  n_pre, n_post = 600, 501          # n_post not divisible by the world size: ragged last range
+  data, indices, indptr, rng = cases.csr_case((n_pre, n_post), 0.05, 5, homo=0.6 if homo else None)
+  events = [(rng.random(n_pre) < r) for r in (0.1, 0.0, 1.0)]
+  return n_pre, n_post, data, indices, indptr, events
+
+
+def test_column_shards_tile_the_matrix():
+  n_pre, n_post, data, indices, indptr, _ = _case()
+  t = [torch.from_numpy(a) for a in (data, indices, indptr)]
+  for world in (1, 2, 3, 8):
+    seen = 0
+    dense = np.zeros((n_pre, n_post), dtype=np.float64)
+    for rank in range(world):
+      d, idx, ptr, (lo, hi) = sharded.shard_csr_by_columns(t[0], t[1], t[2], n_post, rank, world)
+      assert ptr[0] == 0 and ptr[-1] == idx.shape[0] == d.shape[0]
+      assert idx.numel() == 0 or (0 <= idx.min() and idx.max() < hi - lo)
+      seen += idx.shape[0]
+      rows = np.repeat(np.arange(n_pre), np.diff(ptr.numpy()))
+      np.add.at(dense, (rows, idx.numpy() + lo), d.numpy())
+    assert seen == indices.shape[0]
+    want = np.zeros_like(dense)
+    np.add.at(want, (np.repeat(np.arange(n_pre), np.diff(indptr)), indices), data)
+    np.testing.assert_array_equal(dense, want)
+  assert sharded.column_range(10, 3, 4) == (9, 10) and sharded.column_range(10, 0, 1) == (0, 10)
+
+
+def _worker(rank, world, port, homo, out_queue):
+  os.environ['MASTER_ADDR'] = '127.0.0.1'
+  os.environ['MASTER_PORT'] = str(port)
+  dist.init_process_group('gloo', rank=rank, world_size=world)
+  try:
+    n_pre, n_post, data, indices, indptr, events = _case(homo)
+    t = [torch.from_numpy(a) for a in (data, indices, indptr)]
+    d, idx, ptr, rng_cols = sharded.shard_csr_by_columns(t[0], t[1], t[2], n_post, rank, world)
+    op = sharded.ShardedEventCSR(d, idx, ptr, n_pre, rng_cols, local_op=_oracle_op)
+    lo_s, hi_s = op.source_range()
+    results = []
+    for ev in events:
+      for dtype in (np.bool_, np.float32):
+        local = torch.from_numpy(ev[lo_s:hi_s].astype(dtype))
+        results.append(op.step(local).numpy())
+    out_queue.put((rank, rng_cols, results))
+  finally:
+    dist.destroy_process_group()
+
+
+def _run_world(world, homo):
+  ctx = mp.get_context('spawn')
+  q = ctx.Queue()
+  port = _free_port()
+  procs = [ctx.Process(target=_worker, args=(r, world, port, homo, q)) for r in range(world)]
+  for p in procs:
+    p.start()
+  got = [q.get(timeout=120) for _ in range(world)]
+  for p in procs:
+    p.join(timeout=60)
+    assert p.exitcode == 0
+  return sorted(got)
+
+
+def test_two_ranks_reproduce_the_single_device_result():
+  for homo in (False, True):
+    n_pre, n_post, data, indices, indptr, events = _case(homo)
+    got = _run_world(2, homo)
+    k = 0
+    for ev in events:
+      for dtype in (np.bool_, np.float32):
+        want = cpu.event_csr_matvec(data, indices, indptr, ev.astype(dtype), shape=(n_pre, n_post), transpose=True)
+        y = np.concatenate([res[k] for _, _, res in got])
+        assert y.shape == want.shape
+        # same per-target addition order inside a shard as in the whole matrix: bit-exact
+        assert y.tobytes() == want.tobytes()
+        k += 1
+    assert [r for _, r, _ in got] == [(0, 251), (251, 501)]

@@ -424,16 +424,16 @@ def run_ours(args):
     # Tear down in a fixed order: the captured graphs hold NCCL kernels and must go before the
     # communicator.  A process that still cannot finish the teardown within 30 s leaves anyway:
     # the measurement is complete and printed, and a launcher must not wait on it for ever.
-    torch.cuda.synchronize()
-    dist.barrier()
-    graph.reset()
-    warm.reset()
-    torch.cuda.synchronize()
     sys.stdout.flush()
     sys.stderr.flush()
     watchdog = threading.Timer(30.0, lambda: os._exit(0))
     watchdog.daemon = True
     watchdog.start()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph.reset()
+    warm.reset()
+    torch.cuda.synchronize()
     dist.destroy_process_group()
     watchdog.cancel()
 

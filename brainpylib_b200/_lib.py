@@ -5,6 +5,7 @@ The library's entry points are XLA legacy custom-call targets
 torch only supplies device memory and the current stream.
 """
 import ctypes
+import functools
 import os
 
 import torch
@@ -52,6 +53,7 @@ def target(name):
   return fn
 
 
+@functools.lru_cache(maxsize=4096)
 def workspace_bytes(name, opaque):
   return int(lib().bpl_workspace_bytes(name.encode(), opaque, len(opaque)))
 
@@ -78,8 +80,12 @@ def call(name, buffers, opaque, device=None, stream=None):
     raise GPUOperatorNotFound(f'{name} (operands are on {device}, a CUDA device is required)')
   fn = target(name)
   ptrs = (ctypes.c_void_p * len(buffers))(*[None if b is None else b.data_ptr() for b in buffers])
-  with torch.cuda.device(device):
-    if stream is None:
-      stream = torch.cuda.current_stream(device).cuda_stream
+  if stream is None:
+    stream = torch.cuda.current_stream(device).cuda_stream
+  if torch.cuda.current_device() == device.index:
     fn(stream, ptrs, opaque, len(opaque))
-  check_status()
+  else:
+    with torch.cuda.device(device):
+      fn(stream, ptrs, opaque, len(opaque))
+  if _lib.bpl_last_status(None, 0) != 0:
+    check_status()

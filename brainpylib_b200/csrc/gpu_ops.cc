@@ -61,6 +61,7 @@ using namespace bpl;
 extern "C" {
 
 size_t bpl_event_csr_workspace_bytes(uint32_t n_row, int transpose);   // csr_kernels.cu
+size_t bpl_nonzero_workspace_bytes(uint32_t batch_size);               // event_info_kernels.cu
 
 int bpl_last_status(char *message, size_t capacity) {
     if (message != nullptr && capacity > 0) std::snprintf(message, capacity, "%s", g_message);
@@ -92,6 +93,10 @@ size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t o
         if (opaque == nullptr || opaque_len != sizeof(TwoUintOneBoolDescriptor)) return 0;
         const TwoUintOneBoolDescriptor *d = reinterpret_cast<const TwoUintOneBoolDescriptor *>(opaque);
         return bpl_event_csr_workspace_bytes(d->uint_x, d->bool_x ? 1 : 0);
+    }
+    if (std::strncmp(target_name, "nonzero_", 8) == 0) {
+        if (opaque == nullptr || opaque_len != sizeof(DoubleSizeDescriptor)) return 0;
+        return bpl_nonzero_workspace_bytes(reinterpret_cast<const DoubleSizeDescriptor *>(opaque)->size_y);
     }
     return 0;
 }

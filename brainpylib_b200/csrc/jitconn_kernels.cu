@@ -158,6 +158,38 @@ jit_rows_dense_kernel(const T *__restrict__ vector, const unsigned int seed, con
     out[row_i] = sum;
 }
 
+// Version 'v1' of the dense-vector product: a Bernoulli test per (row, column) instead of the
+// geometric skip, `conn_prob` being the raw probability (lib/gpu_jitconn_matvec.cu:10-54, :141-187,
+// :284-331).  One `curand_uniform` per column, the weight drawn only on a connection; a different
+// random matrix from 'v2'.  The input vector is staged through shared memory tile by tile as in the
+// reference (plus the barrier the reference omits before a tile is overwritten).
+template<typename T, int KIND>
+__global__ void __launch_bounds__(JIT_THREADS)
+jit_rows_dense_v1_kernel(const T *__restrict__ vector, const unsigned int seed, const double conn_prob,
+                         const double w1, const double w2, const unsigned int num_row,
+                         const unsigned int num_col, T *__restrict__ out) {
+    __shared__ T tile[JIT_THREADS];
+    const unsigned int idx = threadIdx.x;
+    const unsigned int row_i = blockIdx.x * blockDim.x + idx;
+    curandState state;
+    curand_init(seed + row_i, 0, 0, &state);
+    T sum = 0;
+    for (unsigned int c0 = 0; c0 < num_col; c0 += JIT_THREADS) {
+        const unsigned int n_tile = min(static_cast<unsigned int>(JIT_THREADS), num_col - c0);
+        if (idx < n_tile) tile[idx] = vector[c0 + idx];
+        __syncthreads();
+        for (unsigned int sh_i = 0; sh_i < n_tile; ++sh_i) {
+            if (curand_uniform(&state) < conn_prob) {
+                if (KIND == W_HOMO) sum += tile[sh_i];
+                else if (KIND == W_UNIFORM) sum += tile[sh_i] * (curand_uniform(&state) * w2 + w1);
+                else sum += tile[sh_i] * (curand_normal(&state) * w2 + w1);
+            }
+        }
+        __syncthreads();
+    }
+    if (row_i < num_row) out[row_i] = sum;
+}
+
 // Event input read straight from global memory: lib/gpu_jitconn_event_matvec.cu:81-108
 // (homogeneous: adds the event VALUE), :217-248, :365-396 (weight drawn for every synapse,
 // added when the event is truthy).
@@ -433,6 +465,17 @@ void jit_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, si
     launch_ok();
 }
 
+template<typename T, int KIND>
+void jit_matvec_v1_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    JitArgs a;
+    if (!unpack_jit<KIND>(opaque, opaque_len, a)) return;   // a.log_p holds the raw probability here
+    if (a.n_row == 0) return;
+    jit_rows_dense_v1_kernel<T, KIND><<<blocks_for(a.n_row, JIT_THREADS), JIT_THREADS, 0, stream>>>(
+        static_cast<const T *>(buffers[0]), a.seed, a.log_p, a.w1, a.w2, a.n_row, a.n_col,
+        static_cast<T *>(buffers[1]));
+    launch_ok();
+}
+
 template<typename T, typename E, int KIND>
 bool enable_mask_kernel(size_t bytes) {
     static thread_local int configured_device = -1;
@@ -531,6 +574,15 @@ extern "C" {
 JIT_MATVEC_ALL(homo, W_HOMO)
 JIT_MATVEC_ALL(uniform, W_UNIFORM)
 JIT_MATVEC_ALL(normal, W_NORMAL)
+
+#define JIT_MATVEC_V1(name, T, KIND) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_matvec_v1_impl<T, KIND>(s, b, o, n); }
+JIT_MATVEC_V1(gpu_matvec_prob_homo_v1_float, float, W_HOMO)
+JIT_MATVEC_V1(gpu_matvec_prob_homo_v1_double, double, W_HOMO)
+JIT_MATVEC_V1(gpu_matvec_prob_uniform_v1_float, float, W_UNIFORM)
+JIT_MATVEC_V1(gpu_matvec_prob_uniform_v1_double, double, W_UNIFORM)
+JIT_MATVEC_V1(gpu_matvec_prob_normal_v1_float, float, W_NORMAL)
+JIT_MATVEC_V1(gpu_matvec_prob_normal_v1_double, double, W_NORMAL)
 
 #define JIT_EVENT(name, T, E, KIND, ROWS) \
     void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_event_matvec_impl<T, E, KIND, ROWS>(s, b, o, n); }

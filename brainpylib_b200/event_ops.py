@@ -14,7 +14,7 @@ from . import _lib, gpu_ops
 from .errors import GPUOperatorNotFound
 from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_like
 
-__all__ = ['event_csr_matvec']
+__all__ = ['event_csr_matvec', 'event_info']
 
 _workspaces = {}
 
@@ -168,3 +168,42 @@ def event_csr_matvec(
   if torch.is_grad_enabled() and (data.requires_grad or events.requires_grad):
     return _EventCSRMatvec.apply(data, indices, indptr, events, shape, bool(transpose))
   return event_csr_matvec_raw(data, indices, indptr, events, shape=shape, transpose=bool(transpose))
+
+
+_NONZERO_SUFFIX = {torch.bool: '_bool', torch.int32: '_int', torch.int64: '_long', torch.float32: '_float',
+                   torch.float64: '_double'}
+
+
+def event_info(events: torch.Tensor):
+  """Collect event information: the event indices and the event number
+  (mirrors brainpylib/_src/event_ops/event_info_collection.py:24-45).
+
+  Parameters
+  ----------
+  events: tensor
+    A 1-D vector (bool, int32, int64, float32 or float64); its non-zero entries are the events.
+    A 2-D ``(batch, size)`` array is processed row by row (what ``vmap`` gives in the reference).
+
+  Returns
+  -------
+  res: tuple
+    ``(event_ids, event_num)``: int32 indices of the events in ASCENDING order padded with -1
+    (same shape as ``events``), and their count (shape ``()`` or ``(batch,)``).  The reference's
+    GPU kernel returns the same set of indices in an arbitrary order.
+  """
+  events = as_tensor(events, device_of(events))
+  if events.ndim not in (1, 2):
+    raise TypeError('Only support 1D boolean vector.')
+  if events.dtype not in _NONZERO_SUFFIX:
+    raise ValueError(f'unsupported events dtype {events.dtype}')
+  if events.device.type != 'cuda':
+    raise GPUOperatorNotFound(f'nonzero (operands are on {events.device}, a CUDA device is required)')
+  events = contiguous(events)
+  batch, size = (1, events.shape[0]) if events.ndim == 1 else events.shape
+  name = 'nonzero' + _NONZERO_SUFFIX[events.dtype]
+  opaque = gpu_ops.build_nonzero_descriptor(size, batch)
+  ids = torch.empty(events.shape, dtype=torch.int32, device=events.device)
+  num = torch.empty(batch, dtype=torch.int32, device=events.device)
+  ws = _workspace(events.device, _lib.workspace_bytes(name, opaque))
+  _lib.call(name, [events, ids, num, ws], opaque, device=events.device)
+  return ids, (num[0] if events.ndim == 1 else num)

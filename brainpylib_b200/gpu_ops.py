@@ -5,6 +5,7 @@ functions return the packed opaque bytes.  Here it is a thin layer over the C AB
 ``libbrainpylib_b200.so`` (no pybind11 module is needed).
 """
 import ctypes
+import functools
 
 from . import _lib
 
@@ -37,10 +38,11 @@ def registrations():
   return out
 
 
+@functools.lru_cache(maxsize=4096)
 def _build(fn_name, argtypes, args):
   fn = getattr(_lib.lib(), fn_name)
   fn.restype = ctypes.c_size_t
-  fn.argtypes = list(argtypes) + [ctypes.c_void_p, ctypes.c_size_t]
+  fn.argtypes = list(argtypes) + [ctypes.c_void_p, ctypes.c_size_t]   # descriptors are pure functions of their arguments: cached
   buf = ctypes.create_string_buffer(64)
   n = fn(*args, buf, 64)
   if n == 0:
@@ -56,36 +58,36 @@ def _u32(x):
 
 
 def build_twouint_onebool_descriptor(uint_x, uint_y, bool_x):
-  return _build('bpl_build_twouint_onebool_descriptor', [_U, _U, _I], (_u32(uint_x), _u32(uint_y), int(bool(bool_x))))
+  return _build('bpl_build_twouint_onebool_descriptor', (_U, _U, _I), (_u32(uint_x), _u32(uint_y), int(bool(bool_x))))
 
 
 def build_double_size_descriptor(size_x, size_y):
-  return _build('bpl_build_double_size_descriptor', [_U, _U], (_u32(size_x), _u32(size_y)))
+  return _build('bpl_build_double_size_descriptor', (_U, _U), (_u32(size_x), _u32(size_y)))
 
 
 def build_jitconn_prob_homo_descriptor(n_row, n_col, seed, prob):
-  return _build('bpl_build_jitconn_prob_homo_descriptor', [_U, _U, _U, _F],
+  return _build('bpl_build_jitconn_prob_homo_descriptor', (_U, _U, _U, _F),
                 (_u32(n_row), _u32(n_col), _u32(seed), float(prob)))
 
 
 def build_jitconn_prob_uniform_descriptor(n_row, n_col, seed, prob, w_min, w_range):
-  return _build('bpl_build_jitconn_prob_uniform_descriptor', [_U, _U, _U, _F, _F, _F],
+  return _build('bpl_build_jitconn_prob_uniform_descriptor', (_U, _U, _U, _F, _F, _F),
                 (_u32(n_row), _u32(n_col), _u32(seed), float(prob), float(w_min), float(w_range)))
 
 
 def build_jitconn_prob_normal_descriptor(n_row, n_col, seed, prob, w_mu, w_sigma):
-  return _build('bpl_build_jitconn_prob_normal_descriptor', [_U, _U, _U, _F, _F, _F],
+  return _build('bpl_build_jitconn_prob_normal_descriptor', (_U, _U, _U, _F, _F, _F),
                 (_u32(n_row), _u32(n_col), _u32(seed), float(prob), float(w_mu), float(w_sigma)))
 
 
 def build_matmat_jit_prob_descriptor1(m, k, n, seed, log_p, w1, w2):
-  return _build('bpl_build_matmat_jit_prob_descriptor1', [_U, _U, _U, _U, _F, _F, _F],
+  return _build('bpl_build_matmat_jit_prob_descriptor1', (_U, _U, _U, _U, _F, _F, _F),
                 (_u32(m), _u32(k), _u32(n), _u32(seed), float(log_p), float(w1), float(w2)))
 
 
 def _two(name):
   def build(size_x, size_y):
-    return _build(name, [_U, _U], (_u32(size_x), _u32(size_y)))
+    return _build(name, (_U, _U), (_u32(size_x), _u32(size_y)))
   build.__name__ = name[4:]
   return build
 

@@ -18,6 +18,7 @@ import torch
 
 from . import _lib, gpu_ops
 from ._checks import as_tensor, contiguous, device_of, float_suffix
+from .errors import GPUOperatorNotFound
 
 __all__ = [
   'matvec_prob_conn_homo_weight', 'matvec_prob_conn_uniform_weight', 'matvec_prob_conn_normal_weight',
@@ -40,12 +41,24 @@ def _descriptor(kind, n_row, n_col, seed, conn_prob, w1, w2):
   return gpu_ops.build_jitconn_prob_normal_descriptor(n_row, n_col, seed, p, w1, w2)
 
 
-def matvec_raw(vector, *, kind, w1=0., w2=0., conn_prob, shape, seed, transpose, outdim_parallel, out=None):
-  """Primitive ``matvec_prob_{homo,uniform,normal}`` (version 'v2'): dense input vector.
-  ``w1, w2`` = ``(w_low, w_high - w_low)`` or ``(w_mu, w_sigma)``."""
+def matvec_raw(vector, *, kind, w1=0., w2=0., conn_prob, shape, seed, transpose, outdim_parallel, version='v2',
+               out=None):
+  """Primitive ``matvec_prob_{homo,uniform,normal}``: dense input vector.
+  ``w1, w2`` = ``(w_low, w_high - w_low)`` or ``(w_mu, w_sigma)``.  ``version='v1'`` passes the raw
+  probability in the descriptor (matvec.py:338-343) and exists row-parallel only, as in the reference."""
   n_row, n_col = (shape[1], shape[0]) if transpose else shape
-  opaque = _descriptor(kind, n_row, n_col, seed, conn_prob, w1, w2)
-  name = ('gpu_matvec_prob_' if outdim_parallel else 'gpu_matvec_atomic_prob_') + kind + '_v2' + \
+  if version == 'v1':
+    if not outdim_parallel:
+      raise GPUOperatorNotFound(f'gpu_matvec_atomic_prob_{kind}_v1 (the reference registers no such target either)')
+    if kind == 'homo':
+      opaque = gpu_ops.build_jitconn_prob_homo_descriptor(n_row, n_col, seed, conn_prob)
+    elif kind == 'uniform':
+      opaque = gpu_ops.build_jitconn_prob_uniform_descriptor(n_row, n_col, seed, conn_prob, w1, w2)
+    else:
+      opaque = gpu_ops.build_jitconn_prob_normal_descriptor(n_row, n_col, seed, conn_prob, w1, w2)
+  else:
+    opaque = _descriptor(kind, n_row, n_col, seed, conn_prob, w1, w2)
+  name = ('gpu_matvec_prob_' if outdim_parallel else 'gpu_matvec_atomic_prob_') + kind + '_' + version + \
          float_suffix(vector.dtype)
   if out is None:
     out = torch.empty(n_row, dtype=vector.dtype, device=vector.device)
@@ -135,15 +148,14 @@ def _matvec(vector, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_para
   vector = as_tensor(vector, device_of(vector))
   _check_vector(vector, shape, transpose, 'vector')
   assert version in ['v1', 'v2']
-  if version == 'v1':
-    raise NotImplementedError("version='v1' (dense Bernoulli walk, a different matrix from 'v2') is not built; "
-                              "use version='v2'.")
   if not vector.dtype.is_floating_point:
     vector = vector.to(torch.float32)
   kw = dict(kind=kind, w1=w1, w2=w2, conn_prob=conn_prob, shape=(int(shape[0]), int(shape[1])), seed=_seed(seed),
-            transpose=bool(transpose), outdim_parallel=bool(outdim_parallel))
+            transpose=bool(transpose), outdim_parallel=bool(outdim_parallel), version=version)
   vector = contiguous(vector)
   if torch.is_grad_enabled() and vector.requires_grad:
+    if version == 'v1':
+      raise NotImplementedError("version='v1' has no column-parallel kernel, hence no transpose rule; use 'v2'")
     return _Matvec.apply(vector, kw)
   return matvec_raw(vector, **kw)
 

@@ -104,6 +104,10 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   (brainpylib/_src/sparse_ops/cusparse_matvec.py:266-278; math :195-212).
  *   opaque  DoubleSizeDescriptor{n_row, n_col}; buffers [data, indices, indptr, vector T(n_row), y T(n_col)]
  *
+ * gpu_matvec_prob_{homo,uniform,normal}_v1_{float,double}
+ *   replaces lib/gpu_jitconn_matvec.cu:57-81,190-217,334-360 (lib/gpu_ops.cc:143-148): Bernoulli test per
+ *   (row, column); the descriptor's `prob` field holds the raw connection probability, not its log.
+ *   opaque and buffers as for v2.
  * gpu_matvec{,_atomic}_prob_{homo,uniform,normal}_v2_{float,double}
  *   replaces lib/gpu_jitconn_matvec.cu:115-139,254-281,397-424 and
  *   lib/gpu_jitconn_matvec_atomic.cu:55-78,113-139,174-200 (lib/gpu_ops.cc:151-164)
@@ -115,6 +119,12 @@ void bpl_profile_scatter_events(void *before, void *after);
  * gpu_matmat_prob_prob_{normal,uniform}_{float,double}_v1
  *   replaces lib/gpu_jitconn_matmat.cu:279-317,364-402 (lib/gpu_ops.cc:171-174)
  *   opaque  MatMatJITProbDescriptor1{m,k,n,seed,log_p,w1,w2}; buffers [X T(m,k), Y T(m,n)] row-major
+ *
+ * nonzero_{bool,int,long,float,double}   replaces lib/gpu_event_info.cu:48-118 (lib/gpu_ops.cc:72-76)
+ *   opaque NonZeroDescriptor{event_size, batch_size}
+ *   buffers [events E(batch, size), event_ids i32(batch, size), event_num i32(batch), workspace]
+ *   event_ids: ascending indices of the non-zero entries of each row, padded with -1 (the reference
+ *   returns them in an arbitrary, run-dependent order); workspace: bpl_workspace_bytes() = 4096 B per row.
  *
  * gpu_csr_event_sum_{homo,heter}_{f32,f64}_{i32,i64}   replaces lib/gpu_event_sum.cu:50-117
  *   opaque {pre_size, post_size}; buffers [events bool, indices I, indptr I, values T, y T]
@@ -148,6 +158,9 @@ void bpl_profile_scatter_events(void *before, void *after);
     BPL_FOR_EACH_T(X, csr_matvec_heter_adaptive)                    \
     BPL_FOR_EACH_T(X, csr_matvec_transpose_homo)                    \
     BPL_FOR_EACH_T(X, csr_matvec_transpose_heter)                   \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_homo_v1)                      \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_uniform_v1)                   \
+    BPL_FOR_EACH_T(X, gpu_matvec_prob_normal_v1)                    \
     BPL_FOR_EACH_T(X, gpu_matvec_prob_homo_v2)                      \
     BPL_FOR_EACH_T(X, gpu_matvec_prob_uniform_v2)                   \
     BPL_FOR_EACH_T(X, gpu_matvec_prob_normal_v2)                    \
@@ -164,6 +177,7 @@ void bpl_profile_scatter_events(void *before, void *after);
     X(gpu_matmat_prob_prob_normal_double_v1)                        \
     X(gpu_matmat_prob_prob_uniform_float_v1)                        \
     X(gpu_matmat_prob_prob_uniform_double_v1)                       \
+    X(nonzero_bool) X(nonzero_int) X(nonzero_long) X(nonzero_float) X(nonzero_double) \
     BPL_FOR_EACH_FI(X, gpu_csr_event_sum_homo)                      \
     BPL_FOR_EACH_FI(X, gpu_csr_event_sum_heter)                     \
     BPL_FOR_EACH_FI(X, gpu_coo_event_sum_homo)                      \

@@ -104,6 +104,39 @@ def test_matvec_equals_reference_kernels(cuda, kind, w1, w2, odp, dtype):
 
 
 @needs_ref_gpu
+@pytest.mark.parametrize('kind,w1,w2', KINDS)
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+def test_matvec_v1_equals_reference_kernels(cuda, kind, w1, w2, dtype):
+  """version='v1': a Bernoulli test per (row, column) with the raw probability in the descriptor
+  (lib/gpu_jitconn_matvec.cu:10-54,141-187,284-331)."""
+  g = torch.Generator(device='cpu').manual_seed(14)
+  for shape, prob in [((100, 200), 0.1), ((10, 1000), 0.01), ((1000, 10), 0.4), ((300, 777), 0.5), ((2, 1000), 1.0)]:
+    for transpose in (False, True):
+      n_in = shape[0] if transpose else shape[1]
+      n_out = shape[1] if transpose else shape[0]
+      v = torch.randn(n_in, generator=g, dtype=dtype).to(cuda)
+      if kind == 'homo':
+        y = bpl.matvec_prob_conn_homo_weight(v, 1., conn_prob=prob, shape=shape, seed=5, transpose=transpose,
+                                             version='v1')
+        opaque = gpu_ops.build_jitconn_prob_homo_descriptor(n_out, n_in, 5, prob)
+      elif kind == 'uniform':
+        y = bpl.matvec_prob_conn_uniform_weight(v, w_low=w1, w_high=w1 + w2, conn_prob=prob, shape=shape, seed=5,
+                                                transpose=transpose, version='v1')
+        opaque = gpu_ops.build_jitconn_prob_uniform_descriptor(n_out, n_in, 5, prob, w1, w2)
+      else:
+        y = bpl.matvec_prob_conn_normal_weight(v, w_mu=w1, w_sigma=w2, conn_prob=prob, shape=shape, seed=5,
+                                               transpose=transpose, version='v1')
+        opaque = gpu_ops.build_jitconn_prob_normal_descriptor(n_out, n_in, 5, prob, w1, w2)
+      y_ref = torch.full_like(y, float('nan'))
+      tname = 'float' if dtype == torch.float32 else 'double'
+      ref.gpu_call(f'gpu_matvec_prob_{kind}_v1_{tname}', [v, y_ref], opaque)
+      assert torch.equal(y, y_ref), (shape, transpose, (y - y_ref).abs().max())
+  with pytest.raises(bpl.GPUOperatorNotFound):
+    bpl.matvec_prob_conn_homo_weight(torch.zeros(10, device=cuda), 1., conn_prob=0.1, shape=(5, 10), seed=1,
+                                     outdim_parallel=False, version='v1')
+
+
+@needs_ref_gpu
 def test_mask_kernel_path_equals_reference(cuda):
   """Large enough for the shared-memory bitmask kernel (>= 4096 rows), bool and float events."""
   shape, prob = (20000, 30000), 0.01

@@ -291,16 +291,50 @@ def run_ours(args):
 
   # N > 1: every rank produces the spikes of its own 1/N of the neurons and the dense spike vector is
   # all-gathered (NCCL over NVLink) inside the step; the matrix shard then needs no further exchange.
+  # The spikes of a step are inputs (they do not depend on the previous step's output), so inside the
+  # captured graph the all-gather of step s+1 runs on a second stream while step s is scattered.
   per = n_neurons // world
-  ev_full = torch.empty(n_neurons, dtype=torch.float32, device=device) if world > 1 else None
+  ev_full = [torch.empty(n_neurons, dtype=torch.float32, device=device) for _ in range(2)] if world > 1 else None
+  comm_stream = torch.cuda.Stream(device) if world > 1 else None
+
+  def compute(s, events, out=y):
+    event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], events, shape=shape,
+                                   transpose=True, out=out, workspace=ws)
 
   def step(s, out=y):
     events = ev_dev[s]
     if world > 1:
-      dist.all_gather_into_tensor(ev_full, ev_dev[s, rank * per:(rank + 1) * per])
-      events = ev_full
-    event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], events, shape=shape,
-                                   transpose=True, out=out, workspace=ws)
+      dist.all_gather_into_tensor(ev_full[0], ev_dev[s, rank * per:(rank + 1) * per])
+      events = ev_full[0]
+    compute(s, events, out)
+
+  def run_steps(first, count):
+    """`count` steps on the current stream; with several ranks the gathers are double-buffered on
+    `comm_stream` (event dependencies only, so the whole pattern can be captured in a graph)."""
+    if world == 1:
+      for s in range(first, first + count):
+        compute(s, ev_dev[s])
+      return
+    main = torch.cuda.current_stream(device)
+    gathered, consumed = {}, {}
+    start = torch.cuda.Event()
+    start.record(main)
+    comm_stream.wait_event(start)
+    for i in range(count):
+      s, b = first + i, i % 2
+      with torch.cuda.stream(comm_stream):
+        if i >= 2:
+          comm_stream.wait_event(consumed[i - 2])     # the buffer's previous reader has finished
+        dist.all_gather_into_tensor(ev_full[b], ev_dev[s, rank * per:(rank + 1) * per])
+        gathered[i] = torch.cuda.Event()
+        gathered[i].record(comm_stream)
+      main.wait_event(gathered[i])
+      compute(s, ev_full[b])
+      consumed[i] = torch.cuda.Event()
+      consumed[i].record(main)
+    done = torch.cuda.Event()
+    done.record(comm_stream)
+    main.wait_event(done)
 
   # sanity: one step against a plain torch scatter on the same device
   step(0)
@@ -325,12 +359,10 @@ def run_ours(args):
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=side):
-      for s in range(W, W + K):
-        step(s)
+      run_steps(W, K)
     warm = torch.cuda.CUDAGraph()
     with torch.cuda.graph(warm, stream=side):
-      for s in range(W):
-        step(s)
+      run_steps(0, max(W, 1))
     if W:
       warm.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -377,6 +409,45 @@ def run_ours(args):
       e2e['ms'] = t.item()
     e2e_value = total_ops / (e2e['ms'] * 1e-3)
 
+    # ---- the same steps on the column-blocked format (converted once, outside any timed region) ----
+    blocked = None
+    if world == 1 and not args.no_blocked:
+      t0 = time.time()
+      cb = event_ops.csr_to_column_blocked(work['data'], work['indices'], work['indptr'], shape=shape)
+      torch.cuda.synchronize()
+      convert_s = time.time() - t0
+      yb = torch.empty(shape[1], dtype=torch.float32, device=device)
+      event_ops.event_cbcsr_matvec_raw(cb, ev_dev[0], out=yb, workspace=ws)
+      compute(0, ev_dev[0])
+      torch.cuda.synchronize()
+      cb_err = (yb - y).abs().max().item()
+      if not cb_err < 1e-5 * 1000:
+        raise SystemExit(f'column-blocked result differs from the CSR result: max abs error {cb_err}')
+      g2 = torch.cuda.CUDAGraph()
+      with torch.cuda.graph(g2, stream=side):
+        for s in range(W, W + K):
+          event_ops.event_cbcsr_matvec_raw(cb, ev_dev[s], out=yb, workspace=ws)
+      g2.replay()
+      torch.cuda.synchronize()
+      b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      b0.record()
+      g2.replay()
+      b1.record()
+      torch.cuda.synchronize()
+      cb_ms = b0.elapsed_time(b1)
+      n_act_cb = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
+      # algorithmic bytes of a step in this format: 6 B per active synapse (16-bit id + weight), the block
+      # offsets of every active row, spike scan, zero-fill and write-back of y
+      cb_bytes = 6.0 * n_act_cb * DEGREE + 4.0 * n_act_cb * (cb.n_blocks + 1) + 4.0 * n_neurons + 8.0 * shape[1]
+      hbm_peak = measured_peaks()[0]
+      blocked = {'format': 'column-blocked CSR (event_cbcsr_matvec), converted once per matrix',
+                 'value': sum(ops_per_step[W:W + K]) / (cb_ms * 1e-3), 'unit': UNIT, 'ms_per_step': cb_ms / K,
+                 'block_width': cb.block_width, 'n_blocks': cb.n_blocks, 'convert_seconds': convert_s,
+                 'format_bytes': cb.nbytes(), 'max_abs_diff_vs_csr': cb_err,
+                 'roofline_step': {'algorithmic_bytes': cb_bytes, 'achieved': cb_bytes / (cb_ms / K * 1e-3) / 1e9,
+                                   'frac': cb_bytes / (cb_ms / K * 1e-3) / 1e9 / hbm_peak, 'unit': 'GB/s'}}
+      del cb, g2
+
   peak, peak_src = measured_peaks()
   n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
   s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
@@ -404,7 +475,7 @@ def run_ours(args):
                '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
                'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
                'ranks; each rank owns 1/N of the spike sources; NCCL all-gather of the dense spike vector '
-               'inside every step'},
+               'every step, double-buffered on a second stream (step s+1 gathers while step s scatters)'},
     'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
             'ms_per_step': e2e['ms'] / K},
     'gpu_launches': 2 * K,
@@ -412,6 +483,8 @@ def run_ours(args):
     'clocks': sampler.summary(),
   }
 
+  if blocked is not None:
+    line['column_blocked'] = blocked
   if want_cpu:
     cpu_value, kind, done, seconds = time_cpu_steps(work, 100000, budget_seconds=10.0)
     line['cpu_baseline'] = {'value': cpu_value, 'unit': UNIT, 'cores': 1, 'kind': kind,
@@ -493,6 +566,7 @@ def main():
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
                        '(1 GPU, see brainpylib_b200/config_bench.py)')

@@ -14,7 +14,7 @@ from . import _lib, gpu_ops
 from .errors import GPUOperatorNotFound
 from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_like
 
-__all__ = ['event_csr_matvec', 'event_info']
+__all__ = ['event_csr_matvec', 'event_info', 'ColumnBlockedCSR', 'csr_to_column_blocked', 'event_cbcsr_matvec']
 
 _workspaces = {}
 
@@ -207,3 +207,120 @@ def event_info(events: torch.Tensor):
   ws = _workspace(events.device, _lib.workspace_bytes(name, opaque))
   _lib.call(name, [events, ids, num, ws], opaque, device=events.device)
   return ids, (num[0] if events.ndim == 1 else num)
+
+
+# --------------------------------------------------------------------------------------------------
+# Column-blocked CSR: a second storage format for the transposed event product
+# --------------------------------------------------------------------------------------------------
+# No counterpart in the reference.  The plain CSR scatter is bound by scattered reductions in L2
+# (one 32-byte sector operation per synapse).  Cutting the post-synaptic neurons into blocks narrow
+# enough for one block of the output to live in a CTA's shared memory moves the accumulation out of
+# L2.  The format stays row-major: every CSR row keeps its place and its length, but its entries are
+# grouped by column block (stable, so the CSR order survives inside a group), column ids become
+# 16-bit offsets into their block, and a per-row table says where each block's group starts.  The
+# conversion is done once per matrix; the operator that consumes the format is stateless.
+
+class ColumnBlockedCSR:
+  """``offsets`` int32 ``(n_row, n_blocks + 1)``: ``offsets[r, b] .. offsets[r, b + 1]`` are row ``r``'s
+               synapses that target block ``b`` (absolute positions; ``offsets[r, 0] == indptr[r]``,
+               ``offsets[r, n_blocks] == indptr[r + 1]``),
+  ``cols``    int16 storage of uint16 local column ids (column = ``b * block_width + cols``),
+  ``data``    weights in the same order, ``shape`` the matrix shape, ``block_width`` columns per block."""
+
+  def __init__(self, offsets, cols, data, shape, block_width):
+    self.offsets, self.cols, self.data = offsets, cols, data
+    self.shape = (int(shape[0]), int(shape[1]))
+    self.block_width = int(block_width)
+    self.n_blocks = int(offsets.shape[1]) - 1
+
+  def nbytes(self):
+    return sum(t.numel() * t.element_size() for t in (self.offsets, self.cols, self.data))
+
+
+def default_block_width(n_col, device=None):
+  """Columns per block: as many blocks as give every SM one CTA when each block is shared by 4 CTAs,
+  capped by what fits a CTA's shared memory next to the row-pointer cache (45056 floats = 176 KB)."""
+  sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
+  n_blocks = max(1, sms // 4)
+  width = -(-n_col // n_blocks)
+  width = min(max(width, 1024), 45056)
+  return -(-width // 32) * 32
+
+
+def csr_to_column_blocked(data, indices, indptr, *, shape, block_width=None, rows_per_pass=100_000):
+  """Re-lay a CSR matrix (heterogeneous float32 weights, int32 ids) into :class:`ColumnBlockedCSR`.
+
+  Runs on the device of the operands in passes of ``rows_per_pass`` rows (one stable sort per pass).
+  Needs the matrix to have fewer than 2^31 entries."""
+  n_row, n_col = int(shape[0]), int(shape[1])
+  device = indices.device
+  if block_width is None:
+    block_width = default_block_width(n_col, device)
+  if not (0 < block_width <= 65536):
+    raise ValueError('block_width must be in 1..65536 (local column ids are 16 bits)')
+  nse = int(indices.shape[0])
+  if nse >= 2 ** 31:
+    raise ValueError('more than 2^31 - 1 stored entries')
+  n_blocks = max(1, -(-n_col // block_width))
+  indptr64 = indptr.to(torch.int64)
+  lengths = indptr64[1:] - indptr64[:-1]
+  offsets = torch.empty((n_row, n_blocks + 1), dtype=torch.int32, device=device)
+  cols = torch.empty(nse, dtype=torch.int16, device=device)
+  vals = torch.empty(nse, dtype=data.dtype, device=device)
+  for r0 in range(0, n_row, rows_per_pass):
+    r1 = min(n_row, r0 + rows_per_pass)
+    a, b = int(indptr64[r0]), int(indptr64[r1])
+    idx = indices[a:b].to(torch.int64)
+    blk = idx // block_width
+    row = torch.repeat_interleave(torch.arange(r1 - r0, device=device), lengths[r0:r1])
+    key = row * n_blocks + blk
+    counts = torch.bincount(key, minlength=(r1 - r0) * n_blocks).view(r1 - r0, n_blocks)
+    ends = torch.cumsum(counts.view(-1), 0).view(r1 - r0, n_blocks) + a
+    offsets[r0:r1, 1:] = ends.to(torch.int32)
+    offsets[r0:r1, 0] = indptr64[r0:r1].to(torch.int32)
+    if b > a:
+      order = torch.sort(key, stable=True).indices
+      # uint16 stored in int16: values >= 32768 wrap, the kernel reads them back as unsigned
+      cols[a:b] = (idx - blk * block_width)[order].to(torch.int32).to(torch.int16)
+      vals[a:b] = data[a:b][order]
+      del order
+    del idx, blk, row, key, counts, ends
+  return ColumnBlockedCSR(offsets, cols, vals, shape, block_width)
+
+
+def event_cbcsr_matvec_raw(blocked: ColumnBlockedCSR, events, *, out=None, workspace=None):
+  """``y = A^T events`` on a :class:`ColumnBlockedCSR` (heterogeneous float32 weights; bool or float32
+  events).  Target ``event_cbcsr_matvec_heter_float_{bool,float}``."""
+  n_row, n_col = blocked.shape
+  if events.dtype == torch.bool:
+    name = 'event_cbcsr_matvec_heter_float_bool'
+  elif events.dtype == torch.float32:
+    name = 'event_cbcsr_matvec_heter_float_float'
+  else:
+    raise ValueError('events must be bool or float32')
+  if blocked.data.dtype != torch.float32:
+    raise TypeError('column-blocked CSR holds float32 weights')
+  if events.device.type != 'cuda':
+    raise GPUOperatorNotFound(f'{name} (operands are on {events.device}, a CUDA device is required)')
+  opaque = _cb_descriptor(n_row, n_col, blocked.block_width)
+  if out is None:
+    out = torch.empty(n_col, dtype=torch.float32, device=events.device)
+  if workspace is None:
+    workspace = _workspace(events.device, _lib.workspace_bytes(name, opaque))
+  _lib.call(name, [blocked.data, blocked.cols, blocked.offsets, events, out, workspace], opaque, device=events.device)
+  return out
+
+
+def _cb_descriptor(n_row, n_col, block_width):
+  return gpu_ops.build_triple_size_descriptor(n_row, n_col, block_width)
+
+
+def event_cbcsr_matvec(blocked: ColumnBlockedCSR, events: torch.Tensor) -> torch.Tensor:
+  """Transposed event product ``y[c] = sum of w over the synapses (r, c) with events[r] != 0`` on a
+  matrix converted once with :func:`csr_to_column_blocked`.  Same result as
+  ``event_csr_matvec(data, indices, indptr, events, shape=shape, transpose=True)`` up to the order
+  of the floating-point additions."""
+  events = as_tensor(events, blocked.data.device)
+  if events.ndim != 1 or events.shape[0] != blocked.shape[0]:
+    raise ValueError(f'Shape mismatch, vec ({tuple(events.shape)},) @ mat {blocked.shape}.')
+  return event_cbcsr_matvec_raw(blocked, contiguous(events))

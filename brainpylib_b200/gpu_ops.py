@@ -11,7 +11,7 @@ from . import _lib
 
 __all__ = [
   'registrations', 'target_names',
-  'build_twouint_onebool_descriptor', 'build_double_size_descriptor',
+  'build_twouint_onebool_descriptor', 'build_double_size_descriptor', 'build_triple_size_descriptor',
   'build_jitconn_prob_homo_descriptor', 'build_jitconn_prob_uniform_descriptor',
   'build_jitconn_prob_normal_descriptor', 'build_matmat_jit_prob_descriptor1',
   'build_csr_event_sum_descriptor', 'build_coo_event_sum_descriptor',
@@ -63,6 +63,10 @@ def build_twouint_onebool_descriptor(uint_x, uint_y, bool_x):
 
 def build_double_size_descriptor(size_x, size_y):
   return _build('bpl_build_double_size_descriptor', (_U, _U), (_u32(size_x), _u32(size_y)))
+
+
+def build_triple_size_descriptor(size_x, size_y, size_z):
+  return _build('bpl_build_triple_size_descriptor', (_U, _U, _U), (_u32(size_x), _u32(size_y), _u32(size_z)))
 
 
 def build_jitconn_prob_homo_descriptor(n_row, n_col, seed, prob):

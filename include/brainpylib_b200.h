@@ -57,6 +57,7 @@ bpl_custom_call_t bpl_find_target(const char *name); /* NULL when unknown */
  *      As in the reference, real-valued fields arrive as `float` and are stored as `double`. ---- */
 size_t bpl_build_twouint_onebool_descriptor(uint32_t uint_x, uint32_t uint_y, int bool_x, void *out, size_t cap);
 size_t bpl_build_double_size_descriptor(uint32_t size_x, uint32_t size_y, void *out, size_t cap);
+size_t bpl_build_triple_size_descriptor(uint32_t size_x, uint32_t size_y, uint32_t size_z, void *out, size_t cap);
 size_t bpl_build_jitconn_prob_homo_descriptor(uint32_t n_row, uint32_t n_col, uint32_t seed, float prob,
                                               void *out, size_t cap);
 size_t bpl_build_jitconn_prob_uniform_descriptor(uint32_t n_row, uint32_t n_col, uint32_t seed, float prob,
@@ -93,6 +94,16 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   opaque  TwoUintOneBoolDescriptor{n_row, n_col, transpose}
  *   buffers [data T(1|nse), indices u32(nse), indptr u32(n_row+1), events E, y T, workspace]
  *   workspace: bpl_workspace_bytes() bytes when transpose, none otherwise (slot ignored).
+ *
+ * event_cbcsr_matvec_heter_float_{bool,float}   (no counterpart in the reference)
+ *   y = A^T events on a COLUMN-BLOCKED CSR matrix: the post-synaptic neurons are cut into blocks of
+ *   `block_width` <= 45056 columns; the matrix stays row-major, but the entries of a row are grouped
+ *   by block, hold 16-bit column offsets into their block, and offsets[row][b] .. offsets[row][b + 1]
+ *   delimit row's group for block b.  One block's slice of y is accumulated in shared memory, which
+ *   lifts the scattered-reduction limit of the plain CSR scatter.
+ *   opaque  TripleSizeDescriptor{n_row, n_col, block_width} (bpl_build_triple_size_descriptor)
+ *   buffers [data f32(nse), cols u16(nse), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
+ *   workspace: bpl_workspace_bytes() (as for event_csr_matvec with transpose)
  *
  * csr_matvec_{homo,heter}_{scalar,vector,adaptive}_{float,double}
  *   replaces lib/gpu_csr_matvec.cu:84-141,195-246,505-560 (lib/gpu_ops.cc:79-92); the three
@@ -150,6 +161,7 @@ void bpl_profile_scatter_events(void *before, void *after);
 #define BPL_FOR_EACH_TARGET(X)                                      \
     BPL_FOR_EACH_TE(X, event_csr_matvec_homo)                       \
     BPL_FOR_EACH_TE(X, event_csr_matvec_heter)                      \
+    X(event_cbcsr_matvec_heter_float_bool) X(event_cbcsr_matvec_heter_float_float) \
     BPL_FOR_EACH_T(X, csr_matvec_homo_scalar)                       \
     BPL_FOR_EACH_T(X, csr_matvec_homo_vector)                       \
     BPL_FOR_EACH_T(X, csr_matvec_homo_adaptive)                     \

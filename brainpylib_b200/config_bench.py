@@ -148,7 +148,7 @@ def bench_c4(args, device):
 
 
 def bench_c5(args, device):
-  c = workloads.config_c5()
+  c = workloads.config_c5(n=args.cols) if args.cols else workloads.config_c5()
   X = torch.as_tensor(c['matrix']).to(device)
   m, k = X.shape
   n = c['shape'][1]
@@ -173,6 +173,7 @@ def main(argv=None):
   ap.add_argument('--variant', default=None, choices=[None, 'homo', 'uniform', 'normal'])
   ap.add_argument('--odp', type=int, default=None, choices=[None, 0, 1])
   ap.add_argument('--rows', type=int, default=None, help='c4: number of output rows (default 1e6)')
+  ap.add_argument('--cols', type=int, default=None, help='c5: number of output columns (default 65536)')
   args = ap.parse_args(argv)
   if args.steps is None:
     args.steps = {'c1': 200, 'c2': 40, 'c4': 3, 'c5': 3}[args.config]

@@ -50,6 +50,38 @@ __device__ __forceinline__ bool is_event(uint8_t e) { return e != 0; }
 __device__ __forceinline__ bool is_event(float e) { return e != 0.0f; }
 __device__ __forceinline__ bool is_event(double e) { return e != 0.0; }
 
+// Packs the truthiness of n events into a bitmask (bit i of word i / 32 = event i) held in shared
+// memory, cooperatively by the whole block.  Where the event array is 16-byte aligned each lane reads
+// 16 bytes at a time (16 bools, 4 floats or 2 doubles), so a block needs one or two rounds of loads
+// even for a million events; the unaligned case and the ragged end use one ballot per 32 events.
+template<typename E>
+__device__ __forceinline__ void pack_event_mask(const E *__restrict__ x, const uint32_t n, uint32_t *mask) {
+    constexpr uint32_t PER_LANE = 16 / sizeof(E);          // events per 128-bit load
+    constexpr uint32_t SPAN = 32 * PER_LANE;               // events per warp-wide load
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    const uint32_t n_vec = vec_ok ? (n / SPAN) * SPAN : 0u;
+    for (uint32_t base = warp * SPAN; base < n_vec; base += n_warps * SPAN) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + base + lane * PER_LANE);
+        const E *e = reinterpret_cast<const E *>(&raw);
+        uint32_t bits = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < PER_LANE; ++k) bits |= (is_event(e[k]) ? 1u : 0u) << k;
+        // PER_LANE bits per lane -> 32 / PER_LANE lanes make one word
+        constexpr uint32_t LANES_PER_WORD = 32 / PER_LANE;
+        uint32_t word = bits << (PER_LANE * (lane % LANES_PER_WORD));
+#pragma unroll
+        for (uint32_t o = 1; o < LANES_PER_WORD; o <<= 1) word |= __shfl_xor_sync(FULL_MASK, word, o);
+        if (lane % LANES_PER_WORD == 0) mask[base / 32 + lane / LANES_PER_WORD] = word;
+    }
+    const uint32_t n_words = (n + 31u) >> 5;
+    for (uint32_t w = n_vec / 32 + warp; w < n_words; w += n_warps) {
+        const uint32_t i = w * 32u + lane;
+        const uint32_t bits = __ballot_sync(FULL_MASK, (i < n) && is_event(x[i]));
+        if (lane == 0) mask[w] = bits;
+    }
+}
+
 }  // namespace bpl
 
 #endif  // BPL_CSRC_COMMON_CUH_

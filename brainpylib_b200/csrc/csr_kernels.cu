@@ -192,24 +192,46 @@ row_scatter_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restr
 //                brainpylib/_src/event_ops/event_csr_matvec.py:334-357).
 // EVENT = false: f = x, products accumulated with fused multiply-adds as the reference
 //                `sum += data[e] * x[col]` compiles to (lib/gpu_csr_matvec.cu:163).
-template<typename T, typename X, bool HOMO, bool EVENT, bool VEC>
-__global__ void __launch_bounds__(ROW_THREADS)
+//
+// MASK = true (events only): the block first packs the event vector into a bitmask in shared memory
+// (one ballot per 32 events) and tests bits instead of gathering event bytes through L1/L2; the
+// whole-matrix stream then runs at HBM speed.  Blocks of 1024 threads, mask of n_col / 8 bytes.
+constexpr int GATHER_MASK_THREADS = 1024;
+constexpr uint32_t GATHER_MASK_MAX_BITS = 200u * 1024u * 8u;
+
+template<typename T, typename X, bool HOMO, bool EVENT, bool VEC, bool MASK = false>
+__global__ void __launch_bounds__(MASK ? GATHER_MASK_THREADS : ROW_THREADS)
 row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restrict__ indptr,
                   const T *__restrict__ data, const X *__restrict__ x, const uint32_t n_row,
-                  T *__restrict__ y) {
+                  T *__restrict__ y, const uint32_t n_col = 0) {
+    extern __shared__ uint32_t event_mask[];
     const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warps_per_block = blockDim.x >> 5;
+    if (MASK) {
+        pack_event_mask(x, n_col, event_mask);
+        __syncthreads();
+    }
+    auto hit = [&](uint32_t col) -> bool {
+        if (MASK) return (event_mask[col >> 5] >> (col & 31u)) & 1u;
+        return is_event(x[col]);
+    };
     const uint32_t nse = indptr[n_row];
     const uint32_t mean = n_row ? nse / n_row : 0;
-    // lanes per row: each lane takes 4 entries per step
-    const uint32_t lpr = mean <= 16u ? 4u : (mean <= 32u ? 8u : (mean <= 64u ? 16u : 32u));
+    // Lanes per row: a lane takes 4 consecutive entries per 128-bit load and up to GATHER_UNROLL such
+    // loads per step, so mean / 16 lanes cover an average row in one step.  Few lanes per row means
+    // several rows per warp in flight, which is what hides the pointer -> entries -> gather latency
+    // chain when rows are short.
+    const uint32_t want = (mean + 15u) / 16u;
+    const uint32_t lpr = want <= 4u ? 4u : (want <= 8u ? 8u : (want <= 16u ? 16u : 32u));
     const uint32_t rows_per_warp = 32u / lpr;
     const uint32_t sub = lane / lpr, sl = lane % lpr;
     const T homo_w = HOMO ? data[0] : T(0);
-    const uint64_t n_warps = static_cast<uint64_t>(gridDim.x) * ROW_WARPS;
+    const uint64_t n_warps = static_cast<uint64_t>(gridDim.x) * warps_per_block;
     const uint64_t n_groups = (static_cast<uint64_t>(n_row) + rows_per_warp - 1) / rows_per_warp;
     const uint32_t g_full = nse >> 2;
+    constexpr int GATHER_UNROLL = 4;
 
-    for (uint64_t wg = static_cast<uint64_t>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); wg < n_groups;
+    for (uint64_t wg = static_cast<uint64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); wg < n_groups;
          wg += n_warps) {
         const uint64_t row64 = wg * rows_per_warp + sub;
         const bool live = row64 < n_row;
@@ -219,30 +241,42 @@ row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restri
         uint32_t hits = 0;
         if (VEC) {
             const uint32_t g_begin = start >> 2, g_end = (end + 3u) >> 2;
-            for (uint32_t g = g_begin + sl; g < g_end; g += lpr) {
-                if (g < g_full) {
-                    const uint4 ix = ldg_stream_u4(indices + 4ull * g);
-                    Quad<T> wq;
-                    if (!HOMO) load_quad(data + 4ull * g, wq);
-                    const uint32_t c[4] = {ix.x, ix.y, ix.z, ix.w};
+            for (uint32_t g0 = g_begin + sl; g0 < g_end; g0 += lpr * GATHER_UNROLL) {
+                uint4 ix[GATHER_UNROLL];
+                Quad<T> wq[GATHER_UNROLL];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t pos = 4u * g + e;
-                        if (pos >= start && pos < end) {
-                            if (EVENT) {
-                                if (is_event(x[c[e]])) { if (HOMO) ++hits; else acc += wq.v[e]; }
-                            } else {
-                                acc += (HOMO ? homo_w : wq.v[e]) * static_cast<T>(x[c[e]]);
+                for (int u = 0; u < GATHER_UNROLL; ++u) {
+                    const uint32_t g = g0 + u * lpr;
+                    if (g < g_end && g < g_full) {
+                        ix[u] = ldg_stream_u4(indices + 4ull * g);
+                        if (!HOMO) load_quad(data + 4ull * g, wq[u]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < GATHER_UNROLL; ++u) {
+                    const uint32_t g = g0 + u * lpr;
+                    if (g >= g_end) continue;
+                    if (g < g_full) {
+                        const uint32_t c[4] = {ix[u].x, ix[u].y, ix[u].z, ix[u].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t pos = 4u * g + e;
+                            if (pos >= start && pos < end) {
+                                if (EVENT) {
+                                    if (hit(c[e])) { if (HOMO) ++hits; else acc += wq[u].v[e]; }
+                                } else {
+                                    acc += (HOMO ? homo_w : wq[u].v[e]) * static_cast<T>(x[c[e]]);
+                                }
                             }
                         }
-                    }
-                } else {
-                    for (uint32_t pos = max(4u * g, start); pos < end; ++pos) {
-                        const uint32_t col = indices[pos];
-                        if (EVENT) {
-                            if (is_event(x[col])) { if (HOMO) ++hits; else acc += data[pos]; }
-                        } else {
-                            acc += (HOMO ? homo_w : data[pos]) * static_cast<T>(x[col]);
+                    } else {   // ragged tail of the arrays: element-wise
+                        for (uint32_t pos = max(4u * g, start); pos < end; ++pos) {
+                            const uint32_t col = indices[pos];
+                            if (EVENT) {
+                                if (hit(col)) { if (HOMO) ++hits; else acc += data[pos]; }
+                            } else {
+                                acc += (HOMO ? homo_w : data[pos]) * static_cast<T>(x[col]);
+                            }
                         }
                     }
                 }
@@ -251,7 +285,7 @@ row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restri
             for (uint32_t pos = start + sl; pos < end; pos += lpr) {
                 const uint32_t col = indices[pos];
                 if (EVENT) {
-                    if (is_event(x[col])) { if (HOMO) ++hits; else acc += data[pos]; }
+                    if (hit(col)) { if (HOMO) ++hits; else acc += data[pos]; }
                 } else {
                     acc += (HOMO ? homo_w : data[pos]) * static_cast<T>(x[col]);
                 }
@@ -323,6 +357,29 @@ void event_csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaq
         launch_ok();
     } else {
         if (n_row == 0) return;
+        if (vec && n_col >= 8192u && n_col <= GATHER_MASK_MAX_BITS && n_row >= 4096u) {
+            const size_t smem = static_cast<size_t>((n_col + 31u) >> 5) * 4;
+            static thread_local int configured_device = -1;
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (configured_device != dev) {
+                if (cudaFuncSetAttribute(row_gather_kernel<T, E, HOMO, true, true, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(GATHER_MASK_MAX_BITS / 8)) != cudaSuccess) {
+                    launch_ok();
+                    return;
+                }
+                configured_device = dev;
+            }
+            const int per_sm = smem <= 100u * 1024u ? 2 : 1;
+            const uint64_t need = (static_cast<uint64_t>(n_row) + GATHER_MASK_THREADS / 32 - 1) / (GATHER_MASK_THREADS / 32);
+            const uint64_t cap = static_cast<uint64_t>(sm_count()) * per_sm;
+            const int grid = static_cast<int>(need < cap ? need : cap);
+            row_gather_kernel<T, E, HOMO, true, true, true><<<grid, GATHER_MASK_THREADS, smem, stream>>>(
+                indices, indptr, data, events, n_row, y, n_col);
+            launch_ok();
+            return;
+        }
         const int grid = persistent_blocks(8, n_row);
         if (vec)
             row_gather_kernel<T, E, HOMO, true, true><<<grid, ROW_THREADS, 0, stream>>>(

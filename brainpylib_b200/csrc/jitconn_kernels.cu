@@ -229,22 +229,7 @@ jit_rows_event_mask_kernel(const E *__restrict__ events, const unsigned int seed
                            const double w1, const double w2, const unsigned int num_row,
                            const unsigned int num_col, T *__restrict__ out) {
     extern __shared__ uint32_t mask[];
-    const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const unsigned int n_words = (num_col + 31u) >> 5;
-    // pack: one ballot per 32 events, 8 loads in flight per lane
-    for (unsigned int w0 = warp * 8u; w0 < n_words; w0 += (MASK_THREADS / 32) * 8u) {
-        bool a[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const unsigned int i = (w0 + j) * 32u + lane;
-            a[j] = (i < num_col) && is_event(events[i]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t bits = __ballot_sync(FULL_MASK, a[j]);
-            if (lane == 0 && w0 + j < n_words) mask[w0 + j] = bits;
-        }
-    }
+    pack_event_mask(events, num_col, mask);
     __syncthreads();
 
     for (unsigned int row_i = blockIdx.x * MASK_THREADS + threadIdx.x; row_i < num_row;
@@ -338,11 +323,15 @@ jit_cols_event_kernel(const E *__restrict__ events, const unsigned int seed, con
 // (lib/gpu_jitconn_matmat.cu:236-276 normal, :321-361 uniform).
 // ------------------------------------------------------------------------------------------
 // A thread owns one output column and 32 rows of X, as in the reference, and accumulates
-// `sum[i] += X[row_i][pos] * w` in synapse order (same bits).  What changes is where X comes
-// from: the reference reads X[(m_i + i) * k + pos] from global memory, one 32-byte sector per
-// float; here a K-tile of the 32 rows is staged TRANSPOSED in shared memory ([k][row]), so a
-// synapse reads 32 consecutive floats with 128-bit shared loads.  16-byte chunks of a tile row
-// are XOR-swizzled with the row number so that threads reading different rows spread over banks.
+// `sum += X[row][pos] * w` in synapse order (same bits).  What changes is where X comes from: the
+// reference reads X[(m_i + i) * k + pos] from global memory, one 32-byte sector per float; here a
+// K-tile of the 32 rows is staged TRANSPOSED in shared memory ([k][row]), so a synapse reads 32
+// consecutive floats with 128-bit shared loads.  The lanes of a warp read different tile rows
+// (their synapses sit at unrelated positions), which would put them on the same banks; instead
+// lane l reads the 16-byte chunks of its row in the rotated order (c + l) mod CHUNKS, so the
+// eight lanes served together always touch eight different chunks.  The accumulator register
+// (c, i) of lane l therefore belongs to row ((c + l) mod CHUNKS) * PER_CHUNK + i; the rotation is
+// undone when Y is written.
 constexpr int MM_THREADS = 512;
 constexpr int MM_ROWS = 32;
 
@@ -357,13 +346,14 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
                   T *__restrict__ Y) {
     constexpr int KT = MMTile<T>::KT, CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS], chunk-swizzled
+    T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS]
 
     const unsigned long long n_i64 = static_cast<unsigned long long>(blockIdx.x) * MM_THREADS + threadIdx.x;
     const bool live = n_i64 < n;
     const unsigned int n_i = static_cast<unsigned int>(n_i64);
     const unsigned int m_i = blockIdx.y * MM_ROWS;
     const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool vec_ok = (k % (16 / sizeof(T)) == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
 
     Stream s(seed + n_i, log_p);
     curandState &st = s.st;
@@ -373,14 +363,25 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
     for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
 
     for (unsigned int k0 = 0; k0 < k; k0 += KT) {
-        // stage X[m_i .. m_i+31][k0 .. k0+KT) transposed; a warp reads along k (coalesced)
-        for (unsigned int r = warp; r < MM_ROWS; r += MM_THREADS / 32) {
+        // stage X[m_i .. m_i+31][k0 .. k0+KT) transposed: lane = row of X, so the 32 stores of a warp go
+        // to 32 consecutive words (no bank conflict); each lane reads VEC consecutive k from its own row
+        // (the other half of a touched sector is picked up from L1 by the next iteration)
+        {
+            constexpr int VEC = 16 / sizeof(T);
+            const unsigned int r = lane;
             const bool row_ok = m_i + r < m;
-            const T *src = X + static_cast<size_t>(m_i + r) * k;
-            for (unsigned int kk = lane; kk < KT; kk += 32) {
-                const T v = (row_ok && k0 + kk < k) ? src[k0 + kk] : T(0);
-                const unsigned int chunk = (r / PER_CHUNK) ^ (kk & (CHUNKS - 1));
-                tile[kk * MM_ROWS + chunk * PER_CHUNK + (r % PER_CHUNK)] = v;
+            const T *src = X + static_cast<size_t>(m_i + r) * k + k0;
+            for (unsigned int kk = warp * VEC; kk < KT; kk += (MM_THREADS / 32) * VEC) {
+                T v[VEC];
+                if (vec_ok && row_ok && k0 + kk + VEC <= k) {
+                    const uint4 u = *reinterpret_cast<const uint4 *>(src + kk);
+                    *reinterpret_cast<uint4 *>(v) = u;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) v[q] = (row_ok && k0 + kk + q < k) ? src[kk + q] : T(0);
+                }
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) tile[(kk + q) * MM_ROWS + r] = v[q];
             }
         }
         __syncthreads();
@@ -393,7 +394,7 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
             const T *row = tile + kk * MM_ROWS;
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
-                const unsigned int chunk = c ^ (kk & (CHUNKS - 1));
+                const unsigned int chunk = (c + lane) & (CHUNKS - 1);
                 if (sizeof(T) == 4) {
                     const float4 x = *reinterpret_cast<const float4 *>(row + chunk * PER_CHUNK);
                     sum[c * 4 + 0] += (x.x * rand);
@@ -412,8 +413,14 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < MM_ROWS; ++i)
-            if (m_i + i < m) Y[static_cast<size_t>(m_i + i) * n + n_i] = sum[i];
+        for (int c = 0; c < CHUNKS; ++c) {
+            const unsigned int chunk = (c + lane) & (CHUNKS - 1);
+#pragma unroll
+            for (int i = 0; i < PER_CHUNK; ++i) {
+                const unsigned int row = m_i + chunk * PER_CHUNK + i;
+                if (row < m) Y[static_cast<size_t>(row) * n + n_i] = sum[c * PER_CHUNK + i];
+            }
+        }
     }
 }
 

@@ -111,6 +111,23 @@ def test_event_csr_no_events_and_all_events(cuda, rate, transpose):
     assert not y.any()
 
 
+@pytest.mark.parametrize('homo', [True, False])
+@pytest.mark.parametrize('ev_dtype', [np.bool_, np.float32])
+def test_event_csr_gather_with_shared_memory_event_mask(cuda, homo, ev_dtype):
+  """Large enough (>= 4096 rows, >= 8192 columns) for the gather kernel that keeps the events as a
+  bitmask in shared memory; a column count that is not a multiple of 32."""
+  shape = (6000, 30011)
+  data, indices, indptr, rng = cases.csr_case(shape, 0.004, 23, homo=0.6 if homo else None)
+  for rate in (0.05, 1.0, 0.0):
+    events = cases.events_like(rng, shape[1], rate, ev_dtype)
+    y = run_event(cuda, data, indices, indptr, events, shape, False)
+    want = cpu.event_csr_matvec(data, indices, indptr, events, shape=shape, transpose=False)
+    if homo:
+      assert y.tobytes() == want.tobytes()
+    else:
+      np.testing.assert_allclose(y, want, rtol=1e-5, atol=atol_for(indptr, indices, shape[1], False))
+
+
 def test_event_csr_empty_matrix_and_tiny_shapes(cuda):
   for shape in [(1, 1), (1, 5), (5, 1), (3, 0), (0, 3)]:
     n_row, n_col = shape

@@ -460,7 +460,10 @@ def run_ours(args):
   roofline = {
     'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec>', 'achieved': achieved, 'peak': peak,
     'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
-    'traffic': None, 'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
+    # DRAM bytes per launch: an ncu capture of this kernel on a 4e5-neuron twin read 1.046x its algorithmic
+    # bytes (profiles/row_scatter_kernel_c3_event_csr.md); traffic grows with the active synapses
+    'traffic': 1.046 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
+    'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
     'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
              'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak},
   }

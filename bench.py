@@ -321,20 +321,40 @@ def run_ours(args):
     start.record(main)
     comm_stream.wait_event(start)
     for i in range(count):
-      s, b = first + i, i % 2
+      s = first + i
+      b = i % (exchange.slots if exchange is not None else 2)
       with torch.cuda.stream(comm_stream):
         if i >= 2:
-          comm_stream.wait_event(consumed[i - 2])     # the buffer's previous reader has finished
-        dist.all_gather_into_tensor(ev_full[b], ev_dev[s, rank * per:(rank + 1) * per])
+          comm_stream.wait_event(consumed[i - 2])     # at most one step of run-ahead
+        if exchange is not None:
+          exchange.push(ev_dev[s, rank * per:(rank + 1) * per], b)     # peer stores over NVLink
+        else:
+          dist.all_gather_into_tensor(ev_full[b], ev_dev[s, rank * per:(rank + 1) * per])
         gathered[i] = torch.cuda.Event()
         gathered[i].record(comm_stream)
       main.wait_event(gathered[i])
-      compute(s, ev_full[b])
+      if exchange is not None:
+        exchange.wait(b)                              # bounded wait for every peer's slice
+        compute(s, exchange.events(b))
+      else:
+        compute(s, ev_full[b])
       consumed[i] = torch.cuda.Event()
       consumed[i].record(main)
     done = torch.cuda.Event()
     done.record(comm_stream)
     main.wait_event(done)
+
+  exchange = None
+  if world > 1 and args.exchange == 'push':
+    from brainpylib_b200 import sharded
+    try:
+      exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
+    except Exception as e:   # symmetric memory unavailable: keep the collective and say so
+      log(f'[bench] rank {rank}: push exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gather')
+    ok = torch.tensor([1 if exchange is not None else 0], device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if not int(ok.item()):
+      exchange = None
 
   # sanity: one step against a plain torch scatter on the same device
   step(0)
@@ -383,6 +403,13 @@ def run_ours(args):
       ms = t.item()
     total_ops = sum(ops_per_step[W:W + K])
     value = total_ops / (ms * 1e-3)
+    if exchange is not None:
+      exchange.check()                       # no wait timed out
+      y_last = y.clone()
+      step(W + K - 1)                        # same step through the NCCL path
+      torch.cuda.synchronize()
+      if not torch.allclose(y_last, y, rtol=1e-5, atol=1e-2):
+        raise SystemExit('push exchange: result of the last step differs from the NCCL all-gather path')
 
     # ---- roofline: the scatter kernel alone, timed by events recorded around it ----
     lib = _lib.lib()
@@ -477,8 +504,9 @@ def run_ours(args):
                'l2': 'inputs larger than L2: each step streams a different ~80 MB of the '
                '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
                'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
-               'ranks; each rank owns 1/N of the spike sources; NCCL all-gather of the dense spike vector '
-               'every step, double-buffered on a second stream (step s+1 gathers while step s scatters)'},
+               'ranks; each rank owns 1/N of the spike sources; every step the dense spike vector is assembled by '
+               + ('peer stores over NVLink with bounded waits (push exchange)' if exchange is not None else 'an NCCL all-gather')
+               + ', one step ahead on a second stream (step s+1 is exchanged while step s scatters)'},
     'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
             'ms_per_step': e2e['ms'] / K},
     'gpu_launches': 2 * K,
@@ -570,6 +598,8 @@ def main():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
+  ap.add_argument('--exchange', default='push', choices=['push', 'nccl'],
+                  help='N > 1: how the spike vector is assembled every step (peer stores over NVLink, or NCCL)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
                        '(1 GPU, see brainpylib_b200/config_bench.py)')

@@ -15,7 +15,7 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ['column_range', 'shard_rows_by_columns', 'shard_csr_by_columns', 'ShardedEventCSR']
+__all__ = ['column_range', 'shard_rows_by_columns', 'shard_csr_by_columns', 'ShardedEventCSR', 'PushExchange']
 
 
 def column_range(n_col: int, rank: int, world: int) -> Tuple[int, int]:
@@ -103,3 +103,100 @@ class ShardedEventCSR:
     events = self.gather_events(local_events)
     return self.local_op(self.data, self.indices, self.indptr, events, shape=(self.n_pre, self.hi - self.lo),
                          transpose=True)
+
+
+class PushExchange:
+  """All-gather of the spike vector by peer stores over NVLink instead of a collective.
+
+  Each rank pushes its slice of the event vector into slot ``k`` of every peer's buffer
+  (``bpl_spike_exchange_push``) and every rank then waits, with a bounded number of polls, until
+  all slices of slot ``k`` have arrived (``bpl_spike_exchange_wait``).  The buffers live in torch
+  symmetric memory so that every rank can address every peer's copy; with one rank ordinary device
+  memory is used.  Kernels that follow the wait on the same stream read ``events(k)``, which is
+  local memory.
+
+  Slot discipline: call ``push`` / ``wait`` with ``k = step % slots``.  With ``slots >= 4`` a rank
+  whose push of step ``s + 1`` is ordered after its own consumption of step ``s - 1`` (one step of
+  run-ahead, as in ``bench.py``) can never overwrite a slot that a peer is still reading: a push
+  into slot ``(s + 4) % 4`` needs this rank's step ``s + 2`` finished, which needed every peer's push
+  of step ``s + 2``, which that peer ordered after its own step ``s`` finished.
+
+  ``check()`` raises if any wait timed out (the status word is read from the device: it synchronises).
+  """
+
+  def __init__(self, n_events: int, dtype=torch.float32, device=None, group=None, slots: int = 4,
+               max_polls: int = 5_000_000):
+    import ctypes
+    from . import _lib
+    self._ctypes, self._lib = ctypes, _lib
+    self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+    self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if n_events % self.world != 0:
+      raise ValueError('the number of events must be divisible by the number of ranks')
+    if self.world > 16:
+      raise ValueError('at most 16 ranks')
+    self.slots, self.max_polls = int(slots), int(max_polls)
+    self.n_events, self.dtype = int(n_events), dtype
+    self.device = torch.device('cuda', torch.cuda.current_device()) if device is None else device
+    item = torch.empty(0, dtype=dtype).element_size()
+    self.slice_bytes = (self.n_events // self.world) * item
+    data_bytes = self.slots * self.n_events * item
+    flag_words = self.slots * self.world
+    total_words = (data_bytes + 3) // 4 + flag_words
+    if self.world == 1:
+      self._buf = torch.zeros(total_words, dtype=torch.int32, device=self.device)
+      bases = [self._buf.data_ptr()]
+    else:
+      import torch.distributed._symmetric_memory as symm_mem
+      self._buf = symm_mem.empty(total_words, dtype=torch.int32, device=self.device)
+      self._buf.zero_()
+      self._hdl = symm_mem.rendezvous(self._buf, dist.group.WORLD if group is None else group)
+      bases = [int(p) for p in self._hdl.buffer_ptrs]
+      torch.cuda.synchronize()
+      dist.barrier(group)      # every rank has zeroed its counters before anyone pushes
+    flag_off = ((data_bytes + 3) // 4) * 4
+    self._peer_data = (ctypes.c_void_p * self.world)(*bases)
+    self._peer_flags = (ctypes.c_void_p * self.world)(*[b + flag_off for b in bases])
+    self._flags_ptr = bases[self.rank] + flag_off
+    self._state = torch.zeros(self.slots + 1, dtype=torch.int32, device=self.device)
+    self._data = self._buf[: data_bytes // 4].view(torch.uint8).view(dtype).view(self.slots, self.n_events)
+    lib = _lib.lib()
+    self._push = lib.bpl_spike_exchange_push
+    self._push.restype = None
+    self._push.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
+                           ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    self._wait = lib.bpl_spike_exchange_wait
+    self._wait.restype = None
+    self._wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                           ctypes.c_uint32]
+
+  def _stream(self):
+    return torch.cuda.current_stream(self.device).cuda_stream
+
+  def push(self, local_events: torch.Tensor, slot: int):
+    """Enqueue the push of this rank's slice (``n_events / world`` elements) into ``slot`` of every rank."""
+    if local_events.dtype != self.dtype or local_events.numel() * local_events.element_size() != self.slice_bytes:
+      raise ValueError('local_events must hold n_events / world elements of the exchange dtype')
+    if not local_events.is_contiguous():
+      local_events = local_events.contiguous()
+    self._push(self._stream(), local_events.data_ptr(), self.slice_bytes, self._peer_data, self._peer_flags,
+               self.world, self.rank, int(slot))
+    self._lib.check_status()
+
+  def wait(self, slot: int):
+    """Enqueue the bounded wait for all slices of ``slot``."""
+    self._wait(self._stream(), self._flags_ptr, self._state.data_ptr(), self.world, int(slot), self.slots,
+               self.max_polls)
+    self._lib.check_status()
+
+  def events(self, slot: int) -> torch.Tensor:
+    """The assembled event vector of ``slot`` (local memory, valid after ``wait(slot)``)."""
+    return self._data[slot]
+
+  def timed_out(self) -> bool:
+    return bool(self._state[self.slots].item())
+
+  def check(self):
+    if self.timed_out():
+      raise RuntimeError('spike exchange: a wait ran out of polls (a peer did not push in time); '
+                         'the assembled events of that step are invalid')

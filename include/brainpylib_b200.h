@@ -203,6 +203,19 @@ void bpl_profile_scatter_events(void *before, void *after);
 BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
 #undef BPL_DECLARE_ONE
 
+/* ---- spike exchange between the GPUs of one node (no counterpart in the reference) -----------
+ * push: copies `slice_bytes` bytes at `local` into slot `slot` of every peer's data buffer (at offset
+ *       (slot * world + rank) * slice_bytes) with peer stores, then bumps the peer's arrival counter
+ *       flags[slot * world + rank].  peer_data / peer_flags: HOST arrays of `world` device pointers.
+ * wait: polls this rank's own counters of `slot` until all `world` have passed state[slot]; at most
+ *       `max_polls` polls (~0.2 us each) per source, then state[slots] = 1 (timeout) and it returns:
+ *       the wait is bounded by construction.  state: slots + 1 u32, zero-initialised by the caller.
+ * world <= 16.  Both only enqueue on `stream`. */
+void bpl_spike_exchange_push(bpl_stream_t stream, const void *local, size_t slice_bytes, void *const *peer_data,
+                             void *const *peer_flags, int world, int rank, int slot);
+void bpl_spike_exchange_wait(bpl_stream_t stream, void *flags, void *state, int world, int slot, int slots,
+                             uint32_t max_polls);
+
 /* ---- transposed event product without workspace and without allocation ------------------
  * No counterpart in the reference.  Same computation as event_csr_matvec_heter_float_float
  * with transpose=true, for callers that may neither allocate device memory nor pass the extra

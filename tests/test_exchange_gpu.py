@@ -1,0 +1,46 @@
+"""Single-GPU checks of the spike-exchange kernels (world = 1: the rank pushes to itself): slot
+addressing, the arrival counters across repeated use of a slot, and the bounded wait, which must
+give up with a status instead of spinning when nothing arrives.  Push and wait are separate launches
+on one stream here, so neither ever waits on a kernel that is not already complete or absent."""
+import numpy as np
+import pytest
+import torch
+
+from brainpylib_b200 import sharded
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bool, torch.uint8])
+def test_push_then_wait_roundtrip(cuda, dtype):
+  n = 4096 + 16
+  ex = sharded.PushExchange(n, dtype=dtype, device=cuda, slots=4, max_polls=1000)
+  g = torch.Generator(device='cpu').manual_seed(0)
+  for step in range(11):                      # every slot is reused several times
+    slot = step % ex.slots
+    ev = (torch.rand(n, generator=g) < 0.3)
+    ev = ev.to(dtype) if dtype != torch.float32 else ev.float() * 1.5
+    ev = ev.to(cuda)
+    ex.push(ev, slot)
+    ex.wait(slot)
+    assert torch.equal(ex.events(slot), ev)
+  ex.check()
+
+
+def test_wait_without_push_times_out_and_returns(cuda):
+  ex = sharded.PushExchange(1024, dtype=torch.float32, device=cuda, slots=4, max_polls=200)
+  ex.wait(2)                                   # nothing was pushed into slot 2: the wait must run out
+  torch.cuda.synchronize()                     # ... and the kernel must have returned
+  assert ex.timed_out()
+  with pytest.raises(RuntimeError, match='ran out of polls'):
+    ex.check()
+  # the device is still usable afterwards
+  assert torch.ones(8, device=cuda).sum().item() == 8
+
+
+def test_exchange_argument_checks(cuda):
+  ex = sharded.PushExchange(1024, dtype=torch.float32, device=cuda)
+  with pytest.raises(ValueError):
+    ex.push(torch.zeros(10, device=cuda), 0)
+  with pytest.raises(RuntimeError):
+    ex.wait(9)                                 # slot out of range -> status from the C ABI

@@ -158,13 +158,13 @@ class PushExchange:
     self._peer_data = (ctypes.c_void_p * self.world)(*bases)
     self._peer_flags = (ctypes.c_void_p * self.world)(*[b + flag_off for b in bases])
     self._flags_ptr = bases[self.rank] + flag_off
-    self._state = torch.zeros(self.slots + 1, dtype=torch.int32, device=self.device)
+    self._state = torch.zeros(self.slots + 1 + 16, dtype=torch.int32, device=self.device)
     self._data = self._buf[: data_bytes // 4].view(torch.uint8).view(dtype).view(self.slots, self.n_events)
     lib = _lib.lib()
     self._push = lib.bpl_spike_exchange_push
     self._push.restype = None
     self._push.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
-                           ctypes.c_int, ctypes.c_int, ctypes.c_int]
+                           ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     self._wait = lib.bpl_spike_exchange_wait
     self._wait.restype = None
     self._wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
@@ -180,7 +180,7 @@ class PushExchange:
     if not local_events.is_contiguous():
       local_events = local_events.contiguous()
     self._push(self._stream(), local_events.data_ptr(), self.slice_bytes, self._peer_data, self._peer_flags,
-               self.world, self.rank, int(slot))
+               self._state.data_ptr(), self.world, self.rank, int(slot), self.slots)
     self._lib.check_status()
 
   def wait(self, slot: int):

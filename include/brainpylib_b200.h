@@ -209,10 +209,11 @@ BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
  *       flags[slot * world + rank].  peer_data / peer_flags: HOST arrays of `world` device pointers.
  * wait: polls this rank's own counters of `slot` until all `world` have passed state[slot]; at most
  *       `max_polls` polls (~0.2 us each) per source, then state[slots] = 1 (timeout) and it returns:
- *       the wait is bounded by construction.  state: slots + 1 u32, zero-initialised by the caller.
+ *       the wait is bounded by construction.  state: slots + 1 + 16 u32 of this rank's own memory,
+ *       zero-initialised by the caller (consumed counts, status word, CTA counters of the push).
  * world <= 16.  Both only enqueue on `stream`. */
 void bpl_spike_exchange_push(bpl_stream_t stream, const void *local, size_t slice_bytes, void *const *peer_data,
-                             void *const *peer_flags, int world, int rank, int slot);
+                             void *const *peer_flags, void *state, int world, int rank, int slot, int slots);
 void bpl_spike_exchange_wait(bpl_stream_t stream, void *flags, void *state, int world, int slot, int slots,
                              uint32_t max_polls);
 

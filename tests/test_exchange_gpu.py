@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bool, torch.uint8])
 def test_push_then_wait_roundtrip(cuda, dtype):
-  n = 4096 + 16
+  n = 300_000 + 16          # several CTAs per destination
   ex = sharded.PushExchange(n, dtype=dtype, device=cuda, slots=4, max_polls=1000)
   g = torch.Generator(device='cpu').manual_seed(0)
   for step in range(11):                      # every slot is reused several times
@@ -44,3 +44,5 @@ def test_exchange_argument_checks(cuda):
     ex.push(torch.zeros(10, device=cuda), 0)
   with pytest.raises(RuntimeError):
     ex.wait(9)                                 # slot out of range -> status from the C ABI
+  with pytest.raises(RuntimeError):
+    ex.push(torch.zeros(1024, device=cuda), 7)

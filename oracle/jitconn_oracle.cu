@@ -17,10 +17,15 @@
  *     test can tell a real mismatch from this rounding effect.
  *   - `curand_normal`: the device path uses the fast `__sincosf`, the host path
  *     `sinf`/`cosf`; normal weights agree to about 1e-6, not bitwise.
- * Absolute values of this path are pinned by no reference test (the reference
- * tests are relational only): "parity unpinned" on the CPU side.  The bitwise
- * check of the CUDA kernels is made on the GPU against the reference's own
- * kernels compiled into oracle/_ref/.
+ * The reference's own tests pin no absolute value of this path (they are
+ * relational only).  This oracle is pinned instead against outputs of the
+ * reference's own CUDA kernels: tests/golden/jitconn_reference_gpu.npz holds 93
+ * of them (event / dense / matmat, homo / uniform / normal, both parallel modes),
+ * produced on a B200 by tests/golden/make_golden_jitconn.py, and
+ * tests/test_jitconn_golden.py requires this file to reproduce every one (no
+ * output outside the tolerance over 1.1e6 sampled connections).  The bitwise
+ * check of the CUDA kernels is made on the GPU against the same kernels compiled
+ * into oracle/_ref/ and against the same golden file.
  *
  * Citations are paths inside the brainpylib source tree.
  */

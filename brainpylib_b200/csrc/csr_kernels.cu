@@ -123,40 +123,7 @@ row_scatter_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restr
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t n_list = n_row;
 
-    if (LIST) {  // exclusive prefix over the chunk counts: 4 counts per thread, 256 threads
-        uint32_t c[4];
-        uint32_t s = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t k = threadIdx.x * 4 + j;
-            c[j] = k < n_chunks ? counts[k] : 0u;
-            s += c[j];
-        }
-        uint32_t incl = s;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_up_sync(FULL_MASK, incl, o);
-            if (lane >= static_cast<uint32_t>(o)) incl += t;
-        }
-        if (lane == 31) warp_total[warp] = incl;
-        __syncthreads();
-        uint32_t base = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < ROW_WARPS; ++w) {
-            const uint32_t t = warp_total[w];
-            if (w < static_cast<int>(warp)) base += t;
-            total += t;
-        }
-        uint32_t run = base + incl - s;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            prefix[threadIdx.x * 4 + j] = run;
-            run += c[j];
-        }
-        if (threadIdx.x == 0) prefix[MAX_CHUNKS] = total;
-        __syncthreads();
-        n_list = total;
-    }
+    if (LIST) n_list = chunk_prefix(counts, n_chunks, prefix, warp_total);
     if (n_list == 0) return;
 
     const uint32_t nse = indptr[n_row];
@@ -165,22 +132,29 @@ row_scatter_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restr
     const uint64_t n_items = static_cast<uint64_t>(n_list) * S;
     const uint64_t n_warps = static_cast<uint64_t>(gridDim.x) * ROW_WARPS;
 
-    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * ROW_WARPS + warp; item < n_items; item += n_warps) {
-        const uint32_t li = static_cast<uint32_t>(item / S), h = static_cast<uint32_t>(item % S);
-        uint32_t row = li;
-        if (LIST) {  // chunk c with prefix[c] <= li < prefix[c + 1]
-            uint32_t lo = 0, hi = n_chunks;
-            while (hi - lo > 1) {
-                const uint32_t mid = (lo + hi) >> 1;
-                if (prefix[mid] <= li) lo = mid; else hi = mid;
-            }
-            row = ids[static_cast<uint64_t>(lo) * chunk + (li - prefix[lo])];
-        }
+    // A warp owns the items first, first + n_warps, ...  It resolves up to 32 of them at once, one per lane
+    // (list entry -> row -> row pointers -> piece bounds), so the dependent loads of all its rows overlap,
+    // and then streams the pieces one after the other with all lanes.
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * ROW_WARPS + warp;
+    for (uint64_t base = first; base < n_items; base += n_warps * 32u) {
+        const uint64_t item = base + static_cast<uint64_t>(lane) * n_warps;
+        uint32_t a = 0, b = 0;
         T scale = T(1);
-        if (!LIST) scale = x[row];
-        const uint32_t start = indptr[row], end = indptr[row + 1];
-        const uint32_t a = piece_cut(start, end, h, S), b = piece_cut(start, end, h + 1, S);
-        if (a < b) scatter_span<T, HOMO, !LIST, VEC>(indices, data, homo_w, scale, a, b, nse, y, lane);
+        if (item < n_items) {
+            const uint32_t li = static_cast<uint32_t>(item / S), h = static_cast<uint32_t>(item % S);
+            const uint32_t row = LIST ? list_row(prefix, n_chunks, chunk, ids, li) : li;
+            if (!LIST) scale = x[row];
+            const uint32_t start = indptr[row], end = indptr[row + 1];
+            a = piece_cut(start, end, h, S);
+            b = piece_cut(start, end, h + 1, S);
+        }
+        const uint64_t left = (n_items - base + n_warps - 1) / n_warps;
+        const uint32_t count = left < 32u ? static_cast<uint32_t>(left) : 32u;
+        for (uint32_t t = 0; t < count; ++t) {
+            const uint32_t ta = __shfl_sync(FULL_MASK, a, t), tb = __shfl_sync(FULL_MASK, b, t);
+            const T ts = __shfl_sync(FULL_MASK, scale, t);
+            if (ta < tb) scatter_span<T, HOMO, !LIST, VEC>(indices, data, homo_w, ts, ta, tb, nse, y, lane);
+        }
     }
 }
 

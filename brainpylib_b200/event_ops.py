@@ -17,14 +17,18 @@ from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_li
 __all__ = ['event_csr_matvec', 'event_info', 'ColumnBlockedCSR', 'csr_to_column_blocked', 'event_cbcsr_matvec']
 
 _workspaces = {}
+_retired_workspaces = []
 
 
 def _workspace(device, nbytes):
   """A per-(device, stream) scratch tensor, grown on demand.  Kernels of one stream run
-  in order, so one buffer per stream is safe to reuse."""
+  in order, so one buffer per stream is safe to reuse.  A buffer that is outgrown is kept
+  alive: a captured CUDA graph may still hold its address."""
   key = (device.index, torch.cuda.current_stream(device).cuda_stream)
   ws = _workspaces.get(key)
   if ws is None or ws.numel() < nbytes:
+    if ws is not None:
+      _retired_workspaces.append(ws)
     ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
     _workspaces[key] = ws
   return ws

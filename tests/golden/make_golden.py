@@ -1,7 +1,7 @@
 """Generates tests/golden/stored_matrix.npz from the REFERENCE's own CPU code.
 
-Run where the reference tree is mounted (``BRAINPYLIB_REFERENCE``, default
-/root/reference):  ``python tests/golden/make_golden.py``
+Run where the reference tree is mounted (its location is taken from the environment variable
+``BRAINPYLIB_REFERENCE``):  ``python tests/golden/make_golden.py``
 
 For every case the inputs are rebuilt from a seed (tests/cases.py), the reference's
 compiled C++ kernel (lib/cpu_event_sum.cc, lib/cpu_atomic_sum.cc, lib/cpu_atomic_prod.cc,

@@ -1,7 +1,7 @@
 """Timing of this library's kernels beside the reference's own CUDA kernels (lib/gpu_*.cu compiled for
 sm_100a into oracle/_ref/libref_gpu.so) on the benchmark shapes, same inputs, same GPU, CUDA events,
 best of a few runs.  The assertions are loose floors (a regression guard); the measured ratios are
-printed (run with -s to see them) and recorded in DESIGN.md."""
+printed (run with -s to see them)."""
 import ctypes
 
 import numpy as np

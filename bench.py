@@ -543,51 +543,78 @@ def run_ours(args):
 
 
 def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
-  """Three streams (copy in, compute, copy out) with double buffers: step s+1's spikes are copied in
-  while step s computes and step s-1's result is copied out."""
-  s_in, s_c, s_out = (torch.cuda.Stream(device) for _ in range(3))
+  """End to end through the C ABI with HOST buffers: every step copies that step's spike vector from
+  pinned host memory to the device, calls the custom-call target, and copies the result back to pinned
+  host memory.  Three streams (copy in, compute, copy out) and triple buffers, so step s+1's spikes are
+  copied in while step s computes and step s-1's result is copied out.  The CUDA runtime is driven
+  directly (ctypes) so that Python dispatch stays off the critical path."""
+  import ctypes
+  from brainpylib_b200 import _lib, gpu_ops
+  rt = ctypes.CDLL('libcudart.so.12')
+  rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+  rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint]
+  rt.cudaEventRecord.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+  rt.cudaStreamWaitEvent.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+
+  def check(code):
+    if code != 0:
+      raise SystemExit(f'CUDA runtime call failed with error {code}')
+
+  streams = [torch.cuda.Stream(device) for _ in range(3)]
+  s_in, s_c, s_out = (ctypes.c_void_p(st.cuda_stream) for st in streams)
   n_buf = 3
   ev_buf = [torch.empty(shape[0], dtype=torch.float32, device=device) for _ in range(n_buf)]
+  y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-  done_in = [None] * n_buf
-  done_c = [None] * n_buf
-  done_out = [None] * n_buf
+  name = 'event_csr_matvec_heter_float_float'
+  opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
+  ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
+  target = _lib.target(name)
+  bufs = [(ctypes.c_void_p * 6)(work['data'].data_ptr(), work['indices'].data_ptr(), work['indptr'].data_ptr(),
+                                ev_buf[b].data_ptr(), y_buf[b].data_ptr(), ws.data_ptr()) for b in range(n_buf)]
+
+  def new_event():
+    e = ctypes.c_void_p()
+    check(rt.cudaEventCreateWithFlags(ctypes.byref(e), 2))   # cudaEventDisableTiming
+    return e
+  done_in, done_c, done_out = ([new_event() for _ in range(n_buf)] for _ in range(3))
+  used = [False] * n_buf
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  h2d, d2h = 4 * shape[0], 4 * shape[1]
 
   def run(first, count, timed):
     torch.cuda.synchronize()
+    for b in range(n_buf):
+      used[b] = False
     if timed:
-      with torch.cuda.stream(s_in):
-        e0.record()
+      e0.record(streams[0])
     for i in range(count):
       s, b = first + i, i % n_buf
-      with torch.cuda.stream(s_in):
-        if done_c[b] is not None:
-          s_in.wait_event(done_c[b])       # the buffer's previous reader has finished
-        ev_buf[b].copy_(ev_host[s], non_blocking=True)
-        done_in[b] = torch.cuda.Event()
-        done_in[b].record()
-      with torch.cuda.stream(s_c):
-        s_c.wait_event(done_in[b])
-        yb = bpl.event_csr_matvec(work['data'], work['indices'], work['indptr'], ev_buf[b], shape=shape,
-                                  transpose=True)
-        done_c[b] = torch.cuda.Event()
-        done_c[b].record()
-      with torch.cuda.stream(s_out):
-        s_out.wait_event(done_c[b])
-        y_host[b].copy_(yb, non_blocking=True)
-        yb.record_stream(s_out)
-        done_out[b] = torch.cuda.Event()
-        done_out[b].record()
+      if used[b]:
+        check(rt.cudaStreamWaitEvent(s_in, done_c[b], 0))      # the spike buffer's previous reader has finished
+        check(rt.cudaStreamWaitEvent(s_c, done_out[b], 0))     # the result buffer's previous copy-out has finished
+      check(rt.cudaMemcpyAsync(ev_buf[b].data_ptr(), ev_host[s].data_ptr(), h2d, 1, s_in))
+      check(rt.cudaEventRecord(done_in[b], s_in))
+      check(rt.cudaStreamWaitEvent(s_c, done_in[b], 0))
+      target(s_c, bufs[b], opaque, len(opaque))
+      check(rt.cudaEventRecord(done_c[b], s_c))
+      check(rt.cudaStreamWaitEvent(s_out, done_c[b], 0))
+      check(rt.cudaMemcpyAsync(y_host[b].data_ptr(), y_buf[b].data_ptr(), d2h, 2, s_out))
+      check(rt.cudaEventRecord(done_out[b], s_out))
+      used[b] = True
+    _lib.check_status()
     if timed:
-      with torch.cuda.stream(s_out):
-        s_out.wait_stream(s_c)
-        e1.record()
+      streams[2].wait_stream(streams[1])
+      e1.record(streams[2])
     torch.cuda.synchronize()
 
   run(0, max(W, 1), False)
   run(W, K, True)
-  return {'ms': e0.elapsed_time(e1), 'h2d': 4 * shape[0], 'd2h': 4 * shape[1]}
+  # the last result that reached the host is the last step's
+  last = (K - 1) % n_buf
+  if not torch.isfinite(y_host[last]).all() or float(y_host[last].abs().sum()) == 0.0:
+    raise SystemExit('e2e: the result copied back to the host is empty')
+  return {'ms': e0.elapsed_time(e1), 'h2d': h2d, 'd2h': d2h}
 
 
 def main():

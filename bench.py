@@ -326,14 +326,19 @@ def run_ours(args):
       with torch.cuda.stream(comm_stream):
         if i >= 2:
           comm_stream.wait_event(consumed[i - 2])     # at most one step of run-ahead
-        if exchange is not None:
+        if fused:
+          exchange.push_compacted(ev_dev[s, rank * per:(rank + 1) * per], b)   # compaction + peer stores, one kernel
+        elif exchange is not None:
           exchange.push(ev_dev[s, rank * per:(rank + 1) * per], b)     # peer stores over NVLink
         else:
           dist.all_gather_into_tensor(ev_full[b], ev_dev[s, rank * per:(rank + 1) * per])
         gathered[i] = torch.cuda.Event()
         gathered[i].record(comm_stream)
       main.wait_event(gathered[i])
-      if exchange is not None:
+      if fused:
+        exchange.wait_zero(b, y)                      # bounded wait for every peer's list; zero-fills y
+        exchange.scatter_from_list(work['data'], work['indices'], work['indptr'], b, y, shape[1])
+      elif exchange is not None:
         exchange.wait(b)                              # bounded wait for every peer's slice
         compute(s, exchange.events(b))
       else:
@@ -345,7 +350,7 @@ def run_ours(args):
     main.wait_event(done)
 
   exchange = None
-  if world > 1 and args.exchange == 'push':
+  if world > 1 and args.exchange in ('push', 'fused'):
     from brainpylib_b200 import sharded
     try:
       exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
@@ -355,6 +360,7 @@ def run_ours(args):
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if not int(ok.item()):
       exchange = None
+  fused = exchange is not None and args.exchange == 'fused'
 
   # sanity: one step against a plain torch scatter on the same device
   step(0)
@@ -505,7 +511,9 @@ def run_ours(args):
                '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
                'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
                'ranks; each rank owns 1/N of the spike sources; every step the dense spike vector is assembled by '
-               + ('peer stores over NVLink with bounded waits (push exchange)' if exchange is not None else 'an NCCL all-gather')
+               + ("one kernel that compacts the rank's own spikes and stores the list into every peer over NVLink, bounded waits"
+                  if fused else 'peer stores over NVLink with bounded waits (push exchange)' if exchange is not None
+                  else 'an NCCL all-gather')
                + ', one step ahead on a second stream (step s+1 is exchanged while step s scatters)'},
     'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
             'ms_per_step': e2e['ms'] / K},
@@ -625,7 +633,7 @@ def main():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
-  ap.add_argument('--exchange', default='push', choices=['push', 'nccl'],
+  ap.add_argument('--exchange', default='push', choices=['fused', 'push', 'nccl'],
                   help='N > 1: how the spike vector is assembled every step (peer stores over NVLink, or NCCL)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '

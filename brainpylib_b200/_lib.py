@@ -46,6 +46,9 @@ def target(name):
   fn = _targets.get(name)
   if fn is None:
     addr = lib().bpl_find_target(name.encode())
+    if not addr:   # entry points outside the reference's registry (no XLA name): plain exported symbols
+      sym = getattr(lib(), name, None)
+      addr = ctypes.cast(sym, ctypes.c_void_p).value if sym is not None else None
     if not addr:
       raise GPUOperatorNotFound(name)
     fn = _TARGET_TYPE(addr)

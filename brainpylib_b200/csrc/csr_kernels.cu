@@ -560,3 +560,39 @@ void event_csr_matvec_heter_float_float_noalloc(bpl_stream_t stream, void **buff
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Transposed event product driven by a ready-made spike list (no counterpart in the reference)
+// ------------------------------------------------------------------------------------------
+// The scatter half of event_csr_matvec_heter_float_* on its own, for callers that already hold the
+// compacted spike list in the layout of the workspace (counts[1024], then row ids in 4096-entry chunk
+// segments): the multi-GPU exchange assembles exactly that on every rank.  y must be zero-filled by
+// the caller (the exchange's wait does it).
+//   buffers [data f32(nse), indices u32(nse), indptr u32(n_row + 1), list u32, y f32(n_col)]
+//   opaque  TripleSizeDescriptor{n_row, n_col, n_chunks}
+extern "C" void event_csr_matvec_list_heter_float(bpl_stream_t stream, void **buffers, const char *opaque,
+                                                  size_t opaque_len) {
+    struct Triple { unsigned int n_row, n_col, n_chunks; };
+    const Triple *d = unpack<Triple>(opaque, opaque_len);
+    if (!d) return;
+    if (d->n_chunks > static_cast<unsigned int>(MAX_CHUNKS)) {
+        set_status(BPL_ERR_ARGUMENT, "spike list: more than 1024 chunks");
+        return;
+    }
+    if (d->n_row == 0 || d->n_col == 0 || d->n_chunks == 0) return;
+    const float *data = static_cast<const float *>(buffers[0]);
+    const uint32_t *indices = static_cast<const uint32_t *>(buffers[1]);
+    const uint32_t *indptr = static_cast<const uint32_t *>(buffers[2]);
+    const uint32_t *list = static_cast<const uint32_t *>(buffers[3]);
+    float *y = static_cast<float *>(buffers[4]);
+    const int grid = persistent_blocks(4, static_cast<uint64_t>(d->n_row) * 16);
+    if (g_profile_before) cudaEventRecord(g_profile_before, stream);
+    if (aligned16(indices) && aligned16(data))
+        row_scatter_kernel<float, false, true, true><<<grid, ROW_THREADS, 0, stream>>>(
+            indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
+    else
+        row_scatter_kernel<float, false, true, false><<<grid, ROW_THREADS, 0, stream>>>(
+            indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
+    if (g_profile_after) cudaEventRecord(g_profile_after, stream);
+    launch_ok();
+}

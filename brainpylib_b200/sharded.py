@@ -142,7 +142,17 @@ class PushExchange:
     self.slice_bytes = (self.n_events // self.world) * item
     data_bytes = self.slots * self.n_events * item
     flag_words = self.slots * self.world
-    total_words = (data_bytes + 3) // 4 + flag_words
+    lib = _lib.lib()
+    lib.bpl_spike_list_slot_bytes.restype = ctypes.c_size_t
+    lib.bpl_spike_list_slot_bytes.argtypes = [ctypes.c_uint32, ctypes.c_int]
+    lib.bpl_spike_list_chunks_per_rank.restype = ctypes.c_uint32
+    lib.bpl_spike_list_chunks_per_rank.argtypes = [ctypes.c_uint32]
+    self.n_local = self.n_events // self.world
+    self.list_slot_words = int(lib.bpl_spike_list_slot_bytes(self.n_local, self.world)) // 4
+    self.n_chunks = int(lib.bpl_spike_list_chunks_per_rank(self.n_local)) * self.world
+    data_words = (data_bytes + 3) // 4
+    list_words = self.slots * self.list_slot_words
+    total_words = data_words + flag_words + list_words
     if self.world == 1:
       self._buf = torch.zeros(total_words, dtype=torch.int32, device=self.device)
       bases = [self._buf.data_ptr()]
@@ -154,13 +164,16 @@ class PushExchange:
       bases = [int(p) for p in self._hdl.buffer_ptrs]
       torch.cuda.synchronize()
       dist.barrier(group)      # every rank has zeroed its counters before anyone pushes
-    flag_off = ((data_bytes + 3) // 4) * 4
+    flag_off = data_words * 4
+    list_off = (data_words + flag_words) * 4
+    self._peer_lists = [(ctypes.c_void_p * self.world)(*[b + list_off + k * self.list_slot_words * 4 for b in bases])
+                        for k in range(self.slots)]
+    self._lists = self._buf[data_words + flag_words:].view(self.slots, self.list_slot_words)
     self._peer_data = (ctypes.c_void_p * self.world)(*bases)
     self._peer_flags = (ctypes.c_void_p * self.world)(*[b + flag_off for b in bases])
     self._flags_ptr = bases[self.rank] + flag_off
-    self._state = torch.zeros(self.slots + 1 + 16, dtype=torch.int32, device=self.device)
+    self._state = torch.zeros(self.slots + 1 + 32, dtype=torch.int32, device=self.device)
     self._data = self._buf[: data_bytes // 4].view(torch.uint8).view(dtype).view(self.slots, self.n_events)
-    lib = _lib.lib()
     self._push = lib.bpl_spike_exchange_push
     self._push.restype = None
     self._push.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
@@ -169,6 +182,16 @@ class PushExchange:
     self._wait.restype = None
     self._wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                            ctypes.c_uint32]
+
+    self._push_compacted = lib.bpl_spike_exchange_push_compacted
+    self._push_compacted.restype = None
+    self._push_compacted.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                     ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_int, ctypes.c_int]
+    self._wait_zero = lib.bpl_spike_exchange_wait_zero
+    self._wait_zero.restype = None
+    self._wait_zero.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
 
   def _stream(self):
     return torch.cuda.current_stream(self.device).cuda_stream
@@ -188,6 +211,39 @@ class PushExchange:
     self._wait(self._stream(), self._flags_ptr, self._state.data_ptr(), self.world, int(slot), self.slots,
                self.max_polls)
     self._lib.check_status()
+
+  def push_compacted(self, local_events: torch.Tensor, slot: int):
+    """Fused form: compact this rank's own events (bool or float32) and push the list of global row ids
+    into ``slot`` of every rank's spike list.  Consumers then call ``wait(slot, zero=y)`` and
+    ``scatter_from_list``; nobody scans the assembled vector."""
+    if local_events.numel() != self.n_local or local_events.dtype not in (torch.bool, torch.uint8, torch.float32):
+      raise ValueError('local_events must hold n_events / world bool or float32 elements')
+    if not local_events.is_contiguous():
+      local_events = local_events.contiguous()
+    self._push_compacted(self._stream(), local_events.data_ptr(), int(local_events.dtype == torch.float32),
+                         self.n_local, self.rank * self.n_local, self._peer_lists[int(slot)], self._peer_flags,
+                         self._state.data_ptr(), self.world, self.rank, int(slot), self.slots)
+    self._lib.check_status()
+
+  def wait_zero(self, slot: int, y: torch.Tensor):
+    """Bounded wait for ``slot`` and, in the same launch, zero-fill of the float32 output ``y``."""
+    if y.dtype != torch.float32 or not y.is_contiguous():
+      raise ValueError('y must be a contiguous float32 tensor')
+    self._wait_zero(self._stream(), self._flags_ptr, self._state.data_ptr(), self.world, int(slot), self.slots,
+                    self.max_polls, y.data_ptr(), y.numel())
+    self._lib.check_status()
+
+  def spike_list(self, slot: int) -> torch.Tensor:
+    """The assembled spike list of ``slot`` (local memory, valid after the wait): counts, then row ids."""
+    return self._lists[slot]
+
+  def scatter_from_list(self, data, indices, indptr, slot: int, y: torch.Tensor, n_col: int):
+    """``y += A^T spikes`` on this rank's shard from the list of ``slot`` (``y`` zero-filled by ``wait_zero``)."""
+    from . import gpu_ops
+    opaque = gpu_ops.build_triple_size_descriptor(self.n_events, n_col, self.n_chunks)
+    self._lib.call('event_csr_matvec_list_heter_float', [data, indices, indptr, self._lists[slot], y], opaque,
+                   device=self.device)
+    return y
 
   def events(self, slot: int) -> torch.Tensor:
     """The assembled event vector of ``slot`` (local memory, valid after ``wait(slot)``)."""

@@ -209,13 +209,30 @@ BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
  *       flags[slot * world + rank].  peer_data / peer_flags: HOST arrays of `world` device pointers.
  * wait: polls this rank's own counters of `slot` until all `world` have passed state[slot]; at most
  *       `max_polls` polls (~0.2 us each) per source, then state[slots] = 1 (timeout) and it returns:
- *       the wait is bounded by construction.  state: slots + 1 + 16 u32 of this rank's own memory,
+ *       the wait is bounded by construction.  state: slots + 1 + 17 u32 of this rank's own memory,
  *       zero-initialised by the caller (consumed counts, status word, CTA counters of the push).
  * world <= 16.  Both only enqueue on `stream`. */
 void bpl_spike_exchange_push(bpl_stream_t stream, const void *local, size_t slice_bytes, void *const *peer_data,
                              void *const *peer_flags, void *state, int world, int rank, int slot, int slots);
 void bpl_spike_exchange_wait(bpl_stream_t stream, void *flags, void *state, int world, int slot, int slots,
                              uint32_t max_polls);
+/* Fused form: compaction of this rank's own events pushed straight into every rank's spike LIST (the layout the
+ * scatter consumes: counts[1024], then row ids in 4096-entry chunk segments; rank r owns chunk indices
+ * r * chunks_per_rank ...), so that consumers need no scan: wait_zero (bounded wait + zero-fill of the output
+ * in one launch), then event_csr_matvec_list_heter_float.  peer_lists[p] = peer p's list buffer of this slot
+ * (bpl_spike_list_slot_bytes bytes each); ev_is_float: 0 = bool events, 1 = float32. */
+uint32_t bpl_spike_list_chunks_per_rank(uint32_t n_local);
+size_t bpl_spike_list_slot_bytes(uint32_t n_local, int world);
+void bpl_spike_exchange_push_compacted(bpl_stream_t stream, const void *local_events, int ev_is_float,
+                                       uint32_t n_local, uint32_t row_offset, void *const *peer_lists,
+                                       void *const *peer_flags, void *state, int world, int rank, int slot,
+                                       int slots);
+void bpl_spike_exchange_wait_zero(bpl_stream_t stream, void *flags, void *state, int world, int slot, int slots,
+                                  uint32_t max_polls, void *zero, uint32_t n_zero);
+/* Scatter half of event_csr_matvec_heter_float_* driven by a ready-made spike list; y must be zero-filled.
+ *   buffers [data f32, indices u32, indptr u32(n_row + 1), list u32, y f32(n_col)]
+ *   opaque  TripleSizeDescriptor{n_row, n_col, n_chunks} */
+BPL_DECLARE_TARGET(event_csr_matvec_list_heter_float);
 
 /* ---- transposed event product without workspace and without allocation ------------------
  * No counterpart in the reference.  Same computation as event_csr_matvec_heter_float_float

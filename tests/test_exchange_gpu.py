@@ -46,3 +46,28 @@ def test_exchange_argument_checks(cuda):
     ex.wait(9)                                 # slot out of range -> status from the C ABI
   with pytest.raises(RuntimeError):
     ex.push(torch.zeros(1024, device=cuda), 7)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bool])
+def test_compacted_push_feeds_the_scatter_directly(cuda, dtype):
+  """world = 1: the fused compaction + push assembles the spike list, the wait zero-fills y, and the
+  list-driven scatter gives what event_csr_matvec gives on the same spikes (same kernel, same list)."""
+  import cases
+  import brainpylib_b200 as bpl
+  shape = (9000, 3000)
+  data, indices, indptr, rng = cases.csr_case(shape, 0.01, 17)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=1000)
+  y = torch.full((shape[1],), float('nan'), device=cuda)
+  for step in range(6):
+    slot = step % 4
+    ev = torch.as_tensor(rng.random(shape[0]) < (0.3 if step % 2 else 0.01)).to(cuda)
+    ev = ev if dtype == torch.bool else ev.float() * 2.0
+    ex.push_compacted(ev, slot)
+    ex.wait_zero(slot, y)
+    ex.scatter_from_list(d, ix, ptr, slot, y, shape[1])
+    want = bpl.event_csr_matvec(d, ix, ptr, ev, shape=shape, transpose=True)
+    torch.testing.assert_close(y, want, rtol=1e-5, atol=1e-4)
+    counts = ex.spike_list(slot)[: ex.n_chunks]
+    assert int(counts.sum()) == int((ev != 0).sum())
+  ex.check()

@@ -633,8 +633,9 @@ def main():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
-  ap.add_argument('--exchange', default='push', choices=['fused', 'push', 'nccl'],
-                  help='N > 1: how the spike vector is assembled every step (peer stores over NVLink, or NCCL)')
+  ap.add_argument('--exchange', default='fused', choices=['fused', 'push', 'nccl'],
+                  help='N > 1: how the spikes reach every rank each step: fused (compaction + peer stores of spike lists), '
+                  'push (peer stores of the dense slice) or nccl (all-gather)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
                        '(1 GPU, see brainpylib_b200/config_bench.py)')

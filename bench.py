@@ -315,6 +315,14 @@ def run_ours(args):
       for s in range(first, first + count):
         compute(s, ev_dev[s])
       return
+    if one_launch:
+      mine = slice(rank * per, (rank + 1) * per)
+      exchange.prime(ev_dev[first, mine], y_pair[0])
+      for i in range(count):
+        last = i == count - 1
+        exchange.step(work['data'], work['indices'], work['indptr'], y_pair[i % 2],
+                      None if last else y_pair[(i + 1) % 2], None if last else ev_dev[first + i + 1, mine])
+      return
     main = torch.cuda.current_stream(device)
     gathered, consumed = {}, {}
     start = torch.cuda.Event()
@@ -350,7 +358,7 @@ def run_ours(args):
     main.wait_event(done)
 
   exchange = None
-  if world > 1 and args.exchange in ('push', 'fused'):
+  if world > 1 and args.exchange in ('push', 'fused', 'step'):
     from brainpylib_b200 import sharded
     try:
       exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
@@ -361,6 +369,8 @@ def run_ours(args):
     if not int(ok.item()):
       exchange = None
   fused = exchange is not None and args.exchange == 'fused'
+  one_launch = exchange is not None and args.exchange == 'step'
+  y_pair = [y, torch.empty_like(y)] if one_launch else None
 
   # sanity: one step against a plain torch scatter on the same device
   step(0)
@@ -411,7 +421,7 @@ def run_ours(args):
     value = total_ops / (ms * 1e-3)
     if exchange is not None:
       exchange.check()                       # no wait timed out
-      y_last = y.clone()
+      y_last = (y_pair[(K - 1) % 2] if one_launch else y).clone()
       step(W + K - 1)                        # same step through the NCCL path
       torch.cuda.synchronize()
       if not torch.allclose(y_last, y, rtol=1e-5, atol=1e-2):
@@ -511,13 +521,17 @@ def run_ours(args):
                '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
                'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
                'ranks; each rank owns 1/N of the spike sources; every step the dense spike vector is assembled by '
-               + ("one kernel that compacts the rank's own spikes and stores the list into every peer over NVLink, bounded waits"
+               + ('ONE launch per step: the kernel pushes the compacted spikes of step s+1 into every peer over NVLink, waits '
+                  '(bounded) for the lists of step s and scatters them' if one_launch else
+                  "one kernel that compacts the rank's own spikes and stores the list into every peer over NVLink, bounded waits"
                   if fused else 'peer stores over NVLink with bounded waits (push exchange)' if exchange is not None
                   else 'an NCCL all-gather')
-               + ', one step ahead on a second stream (step s+1 is exchanged while step s scatters)'},
+               + ('' if one_launch else ', one step ahead on a second stream (step s+1 is exchanged while step s scatters)')},
     'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
             'ms_per_step': e2e['ms'] / K},
-    'gpu_launches': 2 * K,
+    # own kernels in the timed graph: scan + scatter per step; push, wait, scan + scatter (dense push);
+    # push, wait, scatter (fused); prime once then one kernel per step (step)
+    'gpu_launches': (K + 1 if one_launch else 3 * K if fused else 4 * K if exchange is not None else 2 * K),
     'roofline': roofline,
     'clocks': sampler.summary(),
   }
@@ -633,7 +647,7 @@ def main():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
-  ap.add_argument('--exchange', default='fused', choices=['fused', 'push', 'nccl'],
+  ap.add_argument('--exchange', default='fused', choices=['step', 'fused', 'push', 'nccl'],
                   help='N > 1: how the spikes reach every rank each step: fused (compaction + peer stores of spike lists), '
                   'push (peer stores of the dense slice) or nccl (all-gather)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],

@@ -29,6 +29,15 @@ __device__ __forceinline__ uint2 ldg_stream_u2(const void *p) {
     return v;
 }
 
+// Reduction without a return value (one L2 operation, nothing travels back), spelled out so that no
+// call site can turn into the value-returning form.
+__device__ __forceinline__ void red_add(float *p, float v) {
+    asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add(double *p, double v) {
+    asm volatile("red.relaxed.gpu.global.add.f64 [%0], %1;" :: "l"(p), "d"(v) : "memory");
+}
+
 template<typename T>
 __device__ __forceinline__ T warp_sum(T v) {
 #pragma unroll

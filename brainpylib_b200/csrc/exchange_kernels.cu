@@ -13,13 +13,14 @@
 // torch's symmetric memory; with world = 1 ordinary device memory will do):
 //   data  [slots][world * slice_bytes]   assembled event vectors
 //   flags [slots][world] u32             arrival counters, zero-initialised once
-//   state [slots + 1 + 17] u32           local: arrivals already consumed per slot, the status word, then the
-//                                        CTA counters of the push kernels (all zero at start)
+//   state [slots + 1 + 32] u32           local: arrivals already consumed per slot, the status word, then the
+//                                        counters of the push and step kernels (all zero at start)
 // Slot reuse: with `slots` >= 4 a producer that runs at most one step ahead of its own consumer
 // cannot overwrite a slot a peer is still reading (see sharded.py).
 #include "abi.h"
 #include "common.cuh"
 #include "spike_scan.cuh"
+#include "row_scatter.cuh"
 
 namespace bpl {
 namespace {
@@ -76,15 +77,17 @@ struct ListTable {
     uint32_t *flags[MAX_WORLD];
 };
 
+// Block-wide: compacts chunk `chunk_in_rank` (<= 4096 events) of this rank's events and stores the ids and
+// the count into every peer's list (`lists[p] + list_offset`) at chunk index `chunk_index`.  Ends with the
+// block's stores issued but not fenced.  `warp_total`: shared, SCAN_THREADS / 32 words.
 template<typename E>
-__global__ void __launch_bounds__(SCAN_THREADS)
-spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, const uint32_t row_offset,
-                       const ListTable peers, const int world, const int rank, const int slot,
-                       const uint32_t chunks_per_rank, uint32_t *__restrict__ cta_counter) {
-    __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+__device__ __forceinline__ void compact_and_push_chunk(const E *__restrict__ events, const uint32_t n_local,
+                                                       const uint32_t row_offset, uint32_t *const *lists,
+                                                       const size_t list_offset, const int world,
+                                                       const uint32_t chunk_in_rank, const uint32_t chunk_index,
+                                                       uint32_t *warp_total) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t chunk_index = rank * chunks_per_rank + blockIdx.x;
-    const uint32_t begin = blockIdx.x * SCAN_TILE;
+    const uint32_t begin = chunk_in_rank * SCAN_TILE;
     const uint32_t end = min(begin + static_cast<uint32_t>(SCAN_TILE), n_local);
     const uint32_t base = begin + warp * SCAN_WARP_SPAN;
     bool act[16];
@@ -99,6 +102,7 @@ spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, con
         bits[k] = __ballot_sync(FULL_MASK, act[k]);
         total += __popc(bits[k]);
     }
+    __syncthreads();               // warp_total may still be read from an earlier use
     if (lane == 0) warp_total[warp] = total;
     __syncthreads();
     uint32_t offset = 0, chunk_total = 0;
@@ -109,51 +113,191 @@ spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, con
         chunk_total += t;
     }
     const uint32_t below = (1u << lane) - 1u;
-    const size_t seg = static_cast<size_t>(MAX_CHUNKS) + static_cast<size_t>(chunk_index) * SCAN_TILE;
+    const size_t seg = list_offset + static_cast<size_t>(MAX_CHUNKS) + static_cast<size_t>(chunk_index) * SCAN_TILE;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
         if (act[k]) {
             const uint32_t at = offset + __popc(bits[k] & below);
             const uint32_t row = row_offset + base + k * 32 + lane;
-            for (int p = 0; p < world; ++p) peers.list[p][seg + at] = row;
+            for (int p = 0; p < world; ++p) lists[p][seg + at] = row;
         }
         offset += __popc(bits[k]);
     }
-    if (threadIdx.x < static_cast<uint32_t>(world)) peers.list[threadIdx.x][chunk_index] = chunk_total;
-    __threadfence_system();
-    __syncthreads();
+    if (threadIdx.x < static_cast<uint32_t>(world)) lists[threadIdx.x][list_offset + chunk_index] = chunk_total;
+}
+
+// Block-wide, after the block's peer stores: the block reports in on `counter`; the last of `n_blocks`
+// reporting blocks resets the counter and bumps this rank's arrival counter of `slot` on every peer.
+// One system-scope fence per block: the barrier orders the block's peer stores before it and the fence is
+// cumulative over them, so they are visible to every GPU before the counter moves.
+__device__ __forceinline__ void publish_arrival(uint32_t *counter, const uint32_t n_blocks, uint32_t *const *flags,
+                                                const int world, const int rank, const int slot) {
     __shared__ bool last;
+    __syncthreads();
     if (threadIdx.x == 0) {
-        const uint32_t done = atomicAdd(cta_counter + MAX_WORLD, 1u);   // counter 16: this kernel's own
-        last = (done == gridDim.x - 1);
-        if (last) cta_counter[MAX_WORLD] = 0u;
+        __threadfence_system();
+        const uint32_t done = atomicAdd(counter, 1u);
+        last = (done == n_blocks - 1);
+        if (last) *counter = 0u;
     }
     __syncthreads();
     if (last && threadIdx.x < static_cast<uint32_t>(world)) {
         __threadfence_system();
-        atomicAdd_system(peers.flags[threadIdx.x] + slot * world + rank, 1u);
+        atomicAdd_system(flags[threadIdx.x] + slot * world + rank, 1u);
     }
+}
+
+// Bounded wait of one warp (lanes < world poll one source each) for generation `expected` of `slot`.
+// Acquire loads at system scope: what a producer wrote before bumping its counter is visible to this
+// thread, and through a barrier or a kernel boundary to whoever runs after it.
+__device__ __forceinline__ bool poll_arrivals(const uint32_t *flags, const int world, const int slot,
+                                              const uint32_t expected, const uint32_t max_polls) {
+    bool ok = true;
+    if (static_cast<int>(threadIdx.x & 31) < world) {
+        const uint32_t *f = flags + slot * world + (threadIdx.x & 31);
+        uint32_t polls = 0;
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+            if (seen >= expected) break;
+            if (++polls > max_polls) { ok = false; break; }
+            __nanosleep(100);
+        }
+    }
+    return __all_sync(FULL_MASK, ok);
+}
+
+template<typename E>
+__global__ void __launch_bounds__(SCAN_THREADS)
+spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, const uint32_t row_offset,
+                       const ListTable peers, const int world, const int rank, const int slot,
+                       const uint32_t chunks_per_rank, uint32_t *__restrict__ cta_counter) {
+    __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    compact_and_push_chunk(events, n_local, row_offset, peers.list, 0, world, blockIdx.x,
+                           rank * chunks_per_rank + blockIdx.x, warp_total);
+    publish_arrival(cta_counter + MAX_WORLD, gridDim.x, peers.flags, world, rank, slot);   // counter 16
+}
+
+// ------------------------------------------------------------------------------------------
+// One launch per simulation step on a sharded matrix: exchange of the NEXT step's spikes fused with
+// the scatter of THIS step's.
+// ------------------------------------------------------------------------------------------
+// The first `pushers` blocks (one per chunk of the rank's own events, at most half the grid) only exchange:
+//   they compact the rank's spikes of step t + 1 and store the list into slot (t + 1) % slots of every
+//   peer (plain peer stores), fence, and publish the arrival on every peer.
+// The other blocks only compute: they wait, bounded, until the lists of step t have arrived from every
+//   rank (pushed by the peers' previous launch, so normally the first poll succeeds) and scatter step t
+//   from the assembled list in local memory into `y_cur` (row_scatter_body).
+// All blocks zero-fill a share of `y_next` (the output buffer of step t + 1; outputs are double-buffered)
+// and take an exit ticket; the last one out advances the step counter t kept in `state`.
+// Nothing here waits on a kernel that has not been launched yet: the lists of step t come from each
+// peer's PREVIOUS launch (or its prime call), which waits only on launches before this one.
+// ctr = state + slots + 1: ctr[17] push counter, ctr[18] exit tickets, ctr[19] step counter t.
+constexpr int CTR_STEP_PUSH = 17, CTR_STEP_EXIT = 18, CTR_STEP_T = 19;
+
+// The exchange half of the step kernel, kept out of line (and everything it needs re-derived from the
+// kernel parameters after it) so that it takes no registers from the scatter loop, which wants all 64 a
+// thread can have at four blocks per SM for its loads in flight.  Returns through `arrived` (shared)
+// whether this block should scatter (false for pushing blocks and after a timeout, which is recorded).
+template<typename E>
+__device__ __noinline__ void step_exchange(float *__restrict__ y_next, const uint32_t n_out,
+                                           const E *__restrict__ next_events, const uint32_t n_local,
+                                           const uint32_t row_offset, const uint32_t chunks_per_rank,
+                                           const ListTable &peers, const size_t slot_words, uint32_t *state,
+                                           const int world, const int rank, const int slots,
+                                           const uint32_t max_polls, const uint32_t pushers, bool *arrived,
+                                           uint32_t *warp_total) {
+    uint32_t *ctr = state + slots + 1;
+    const uint32_t t = ctr[CTR_STEP_T];
+    const int slot = static_cast<int>(t % slots), next_slot = static_cast<int>((t + 1u) % slots);
+    const uint32_t expected = t / slots + 1u;
+    if (y_next != nullptr)
+        for (uint32_t i = blockIdx.x * ROW_THREADS + threadIdx.x; i < n_out; i += gridDim.x * ROW_THREADS)
+            y_next[i] = 0.0f;
+    if (blockIdx.x < pushers) {
+        for (uint32_t c = blockIdx.x; c < chunks_per_rank; c += pushers)
+            compact_and_push_chunk(next_events, n_local, row_offset, peers.list,
+                                   static_cast<size_t>(next_slot) * slot_words, world, c,
+                                   rank * chunks_per_rank + c, warp_total);
+        publish_arrival(ctr + CTR_STEP_PUSH, pushers, peers.flags, world, rank, next_slot);
+        if (threadIdx.x == 0) *arrived = false;
+    } else if (threadIdx.x < 32) {
+        const bool ok = poll_arrivals(peers.flags[rank], world, slot, expected, max_polls);
+        if (threadIdx.x == 0) {
+            *arrived = ok;
+            if (!ok) state[slots] = 1u;        // timed out: the output of this step must not be trusted
+        }
+    }
+    __syncthreads();
+}
+
+template<typename E, bool VEC>
+__global__ void __launch_bounds__(ROW_THREADS, 4)
+sharded_step_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restrict__ indptr,
+                    const float *__restrict__ data, const uint32_t n_row, float *__restrict__ y_cur,
+                    float *__restrict__ y_next, const uint32_t n_out, const E *__restrict__ next_events,
+                    const uint32_t n_local, const uint32_t row_offset, const uint32_t chunks_per_rank,
+                    const __grid_constant__ ListTable peers, const size_t slot_words, uint32_t *state,
+                    const int world, const int rank, const int slots, const uint32_t max_polls) {
+    __shared__ uint32_t prefix[MAX_CHUNKS + 1];
+    __shared__ uint32_t warp_total[ROW_WARPS];
+    __shared__ bool arrived;
+    const uint32_t pushers = next_events == nullptr ? 0u : min(chunks_per_rank, gridDim.x / 2u);
+    step_exchange(y_next, n_out, next_events, n_local, row_offset, chunks_per_rank, peers, slot_words, state, world,
+                  rank, slots, max_polls, pushers, &arrived, warp_total);
+    if (arrived) {
+        const uint32_t slot = state[slots + 1 + CTR_STEP_T] % slots;
+        const uint32_t *list = peers.list[rank] + static_cast<size_t>(slot) * slot_words;
+        row_scatter_body<float, false, true, VEC>(indices, indptr, data, nullptr, n_row, SCAN_TILE,
+                                                  chunks_per_rank * world, list, list + MAX_CHUNKS, y_cur, prefix,
+                                                  warp_total, blockIdx.x - pushers, gridDim.x - pushers);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t *ctr = state + slots + 1;
+        const uint32_t done = atomicAdd(ctr + CTR_STEP_EXIT, 1u);
+        if (done == gridDim.x - 1) {           // every block has read t and finished
+            const uint32_t t = ctr[CTR_STEP_T];
+            ctr[CTR_STEP_EXIT] = 0u;
+            state[t % slots] = t / slots + 1u;
+            ctr[CTR_STEP_T] = t + 1u;
+        }
+    }
+}
+
+// Pushes the spikes of the step the counter points at (the first step of a run) and zero-fills its output.
+template<typename E>
+__global__ void __launch_bounds__(SCAN_THREADS)
+sharded_prime_kernel(const E *__restrict__ events, const uint32_t n_local, const uint32_t row_offset,
+                     const uint32_t chunks_per_rank, const ListTable peers, const size_t slot_words,
+                     uint32_t *state, const int world, const int rank, const int slots,
+                     float *__restrict__ y_first, const uint32_t n_out) {
+    __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    uint32_t *ctr = state + slots + 1;
+    const int slot = static_cast<int>(ctr[CTR_STEP_T] % slots);
+    for (uint32_t i = blockIdx.x * SCAN_THREADS + threadIdx.x; i < n_out; i += gridDim.x * SCAN_THREADS)
+        y_first[i] = 0.0f;
+    compact_and_push_chunk(events, n_local, row_offset, peers.list, static_cast<size_t>(slot) * slot_words, world,
+                           blockIdx.x, rank * chunks_per_rank + blockIdx.x, warp_total);
+    publish_arrival(ctr + CTR_STEP_PUSH, gridDim.x, peers.flags, world, rank, slot);
 }
 
 // grid > 1: the extra blocks only zero-fill `zero` (the consumer's output vector) while block 0 polls.
 __global__ void spike_wait_kernel(uint32_t *__restrict__ flags, uint32_t *__restrict__ state, const int world,
                                   const int slot, const int slots, const uint32_t max_polls,
                                   float *__restrict__ zero, const uint32_t n_zero) {
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_zero; i += gridDim.x * blockDim.x) zero[i] = 0.0f;
-    if (blockIdx.x != 0 || threadIdx.x >= 32) return;
-    const int src = threadIdx.x;
-    const uint32_t expected = state[slot] + 1u;
-    bool ok = true;
-    if (src < world) {
-        const volatile uint32_t *f = flags + slot * world + src;
-        uint32_t polls = 0;
-        while (*f < expected) {
-            if (++polls > max_polls) { ok = false; break; }
-            __nanosleep(200);
+    if (gridDim.x > 1) {
+        if (blockIdx.x != 0) {      // blocks 1.. zero-fill; block 0 only polls, with no stores of its own in flight
+            for (uint32_t i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < n_zero; i += (gridDim.x - 1) * blockDim.x)
+                zero[i] = 0.0f;
+            return;
         }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n_zero; i += blockDim.x) zero[i] = 0.0f;
     }
-    __threadfence_system();   // acquire: what the producers wrote before bumping is visible from here on
-    const bool all_ok = __all_sync(FULL_MASK, ok);
+    if (threadIdx.x >= 32) return;
+    const uint32_t expected = state[slot] + 1u;
+    const bool all_ok = poll_arrivals(flags, world, slot, expected, max_polls);
     if (threadIdx.x == 0) {
         if (all_ok) state[slot] = expected;
         else state[slots] = 1u;   // timed out: the data of this slot must not be trusted
@@ -248,6 +392,72 @@ void bpl_spike_exchange_push_compacted(bpl_stream_t stream, const void *local_ev
     else
         spike_scan_push_kernel<uint8_t><<<cpr, SCAN_THREADS, 0, stream>>>(
             static_cast<const uint8_t *>(local_events), n_local, row_offset, t, world, rank, slot, cpr, counters);
+    launch_ok();
+}
+
+// ---- one launch per step on a sharded matrix (sharded_step_kernel) ----
+// peer_lists[p] / peer_flags[p]: peer p's list buffer (slot 0; slots are slot_bytes apart) and flag array.
+// The step counter lives in `state`, so the same call sequence can be captured in a CUDA graph and replayed.
+
+static bool step_arguments_ok(uint32_t n_local, int world, int rank, int slots, const void *state) {
+    const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
+    if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world || slots < 4 || state == nullptr ||
+        n_local == 0 || static_cast<uint64_t>(cpr) * world > MAX_CHUNKS) {
+        set_status(BPL_ERR_ARGUMENT,
+                   "sharded step: world 1..16, rank < world, slots >= 4, at most 1024 chunks of 4096 events in total");
+        return false;
+    }
+    return true;
+}
+
+static ListTable list_table(void *const *peer_lists, void *const *peer_flags, int world) {
+    ListTable t;
+    for (int p = 0; p < MAX_WORLD; ++p) {
+        t.list[p] = p < world ? static_cast<uint32_t *>(peer_lists[p]) : nullptr;
+        t.flags[p] = p < world ? static_cast<uint32_t *>(peer_flags[p]) : nullptr;
+    }
+    return t;
+}
+
+// Before the first step of a run: push the spikes of that step and zero-fill its output vector.
+void bpl_sharded_prime(bpl_stream_t stream, const void *events, int ev_is_float, uint32_t n_local,
+                       uint32_t row_offset, void *const *peer_lists, size_t slot_bytes, void *const *peer_flags,
+                       void *state, int world, int rank, int slots, void *y_first, uint32_t n_out) {
+    if (!step_arguments_ok(n_local, world, rank, slots, state)) return;
+    const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
+    const ListTable t = list_table(peer_lists, peer_flags, world);
+    if (ev_is_float)
+        sharded_prime_kernel<float><<<cpr, SCAN_THREADS, 0, stream>>>(
+            static_cast<const float *>(events), n_local, row_offset, cpr, t, slot_bytes / 4,
+            static_cast<uint32_t *>(state), world, rank, slots, static_cast<float *>(y_first), n_out);
+    else
+        sharded_prime_kernel<uint8_t><<<cpr, SCAN_THREADS, 0, stream>>>(
+            static_cast<const uint8_t *>(events), n_local, row_offset, cpr, t, slot_bytes / 4,
+            static_cast<uint32_t *>(state), world, rank, slots, static_cast<float *>(y_first), n_out);
+    launch_ok();
+}
+
+// One step: y_cur (already zero) += A_shard^T spikes(t) from the assembled list; pushes `next_events`
+// (this rank's spikes of step t + 1; may be null at the end of a run) and zero-fills `y_next` (may be null).
+void bpl_sharded_step(bpl_stream_t stream, const void *data, const void *indices, const void *indptr,
+                      uint32_t n_row, uint32_t n_out, void *y_cur, void *y_next, const void *next_events,
+                      int ev_is_float, uint32_t n_local, uint32_t row_offset, void *const *peer_lists,
+                      size_t slot_bytes, void *const *peer_flags, void *state, int world, int rank, int slots,
+                      uint32_t max_polls) {
+    if (!step_arguments_ok(n_local, world, rank, slots, state)) return;
+    const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
+    const ListTable t = list_table(peer_lists, peer_flags, world);
+    const int grid = sm_count() * 4;
+    const bool vec = aligned16(indices) && aligned16(data);
+#define BPL_STEP_LAUNCH(E, VEC)                                                                                  \
+    sharded_step_kernel<E, VEC><<<grid, ROW_THREADS, 0, stream>>>(                                               \
+        static_cast<const uint32_t *>(indices), static_cast<const uint32_t *>(indptr),                           \
+        static_cast<const float *>(data), n_row, static_cast<float *>(y_cur), static_cast<float *>(y_next),      \
+        n_out, static_cast<const E *>(next_events), n_local, row_offset, cpr, t, slot_bytes / 4,                 \
+        static_cast<uint32_t *>(state), world, rank, slots, max_polls)
+    if (ev_is_float) { if (vec) BPL_STEP_LAUNCH(float, true); else BPL_STEP_LAUNCH(float, false); }
+    else             { if (vec) BPL_STEP_LAUNCH(uint8_t, true); else BPL_STEP_LAUNCH(uint8_t, false); }
+#undef BPL_STEP_LAUNCH
     launch_ok();
 }
 

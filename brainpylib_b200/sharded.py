@@ -193,6 +193,18 @@ class PushExchange:
     self._wait_zero.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                 ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
 
+    self._prime = lib.bpl_sharded_prime
+    self._prime.restype = None
+    self._prime.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                            ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                            ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint32]
+    self._step = lib.bpl_sharded_step
+    self._step.restype = None
+    self._step.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32,
+                           ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                           ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                           ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint32]
+
   def _stream(self):
     return torch.cuda.current_stream(self.device).cuda_stream
 
@@ -244,6 +256,37 @@ class PushExchange:
     self._lib.call('event_csr_matvec_list_heter_float', [data, indices, indptr, self._lists[slot], y], opaque,
                    device=self.device)
     return y
+
+  # ---- one launch per step: exchange of the next step's spikes fused with this step's scatter ----
+  def _check_events(self, ev):
+    if ev.numel() != self.n_local or ev.dtype not in (torch.bool, torch.uint8, torch.float32):
+      raise ValueError('events must hold n_events / world bool or float32 elements')
+    return ev if ev.is_contiguous() else ev.contiguous()
+
+  def prime(self, local_events: torch.Tensor, y_first: torch.Tensor):
+    """Before the first ``step`` of a run: pushes this rank's spikes of that step and zero-fills its output."""
+    ev = self._check_events(local_events)
+    self._prime(self._stream(), ev.data_ptr(), int(ev.dtype == torch.float32), self.n_local,
+                self.rank * self.n_local, self._peer_lists[0], self.list_slot_words * 4, self._peer_flags,
+                self._state.data_ptr(), self.world, self.rank, self.slots, y_first.data_ptr(), y_first.numel())
+    self._lib.check_status()
+
+  def step(self, data, indices, indptr, y_cur: torch.Tensor, y_next, next_events):
+    """One simulation step in one launch: ``y_cur += A_shard^T spikes(t)`` from the lists every rank pushed for
+    step t, while this rank's spikes of step t + 1 (``next_events``, or None at the end of a run) go out to
+    every peer and ``y_next`` (or None) is zero-filled.  ``y_cur`` must already be zero: ``prime`` clears the
+    first one, every ``step`` the next.  The step counter lives on the device, so captured steps replay."""
+    ev = None if next_events is None else self._check_events(next_events)
+    for t in (y_cur, y_next):
+      if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+        raise ValueError('outputs must be contiguous float32 tensors')
+    self._step(self._stream(), data.data_ptr(), indices.data_ptr(), indptr.data_ptr(), self.n_events, y_cur.numel(),
+               y_cur.data_ptr(), None if y_next is None else y_next.data_ptr(),
+               None if ev is None else ev.data_ptr(), int(ev is not None and ev.dtype == torch.float32),
+               self.n_local, self.rank * self.n_local, self._peer_lists[0], self.list_slot_words * 4,
+               self._peer_flags, self._state.data_ptr(), self.world, self.rank, self.slots, self.max_polls)
+    self._lib.check_status()
+    return y_cur
 
   def events(self, slot: int) -> torch.Tensor:
     """The assembled event vector of ``slot`` (local memory, valid after ``wait(slot)``)."""

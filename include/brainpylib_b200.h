@@ -229,6 +229,24 @@ void bpl_spike_exchange_push_compacted(bpl_stream_t stream, const void *local_ev
                                        int slots);
 void bpl_spike_exchange_wait_zero(bpl_stream_t stream, void *flags, void *state, int world, int slot, int slots,
                                   uint32_t max_polls, void *zero, uint32_t n_zero);
+
+/* One launch per simulation step on a column-sharded matrix (no reference counterpart): the kernel pushes
+ * this rank's spikes of step t + 1 as a compacted list into every peer (peer stores), zero-fills y_next,
+ * waits (bounded by max_polls) for the lists of step t from every rank, and scatters step t into y_cur,
+ * which must already be zero (bpl_sharded_prime zero-fills the first one).  The step counter t lives in
+ * `state` (slots + 1 + 32 zero-initialised uint32), so a captured sequence of steps can be replayed.
+ * peer_lists[p] / peer_flags[p]: peer p's list buffer (slots x slot_bytes, see bpl_spike_list_slot_bytes)
+ * and arrival counters (slots x world uint32, zero-initialised).  slots >= 4.  A timeout sets the status
+ * word state[slots] to 1 and skips the scatter.  An exchange object is driven either by these two calls or
+ * by the push / wait calls above, not by both. */
+void bpl_sharded_prime(bpl_stream_t stream, const void *events, int ev_is_float, uint32_t n_local,
+                       uint32_t row_offset, void *const *peer_lists, size_t slot_bytes, void *const *peer_flags,
+                       void *state, int world, int rank, int slots, void *y_first, uint32_t n_out);
+void bpl_sharded_step(bpl_stream_t stream, const void *data, const void *indices, const void *indptr,
+                      uint32_t n_row, uint32_t n_out, void *y_cur, void *y_next, const void *next_events,
+                      int ev_is_float, uint32_t n_local, uint32_t row_offset, void *const *peer_lists,
+                      size_t slot_bytes, void *const *peer_flags, void *state, int world, int rank, int slots,
+                      uint32_t max_polls);
 /* Scatter half of event_csr_matvec_heter_float_* driven by a ready-made spike list; y must be zero-filled.
  *   buffers [data f32, indices u32, indptr u32(n_row + 1), list u32, y f32(n_col)]
  *   opaque  TripleSizeDescriptor{n_row, n_col, n_chunks} */

@@ -71,3 +71,49 @@ def test_compacted_push_feeds_the_scatter_directly(cuda, dtype):
     counts = ex.spike_list(slot)[: ex.n_chunks]
     assert int(counts.sum()) == int((ev != 0).sum())
   ex.check()
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bool])
+def test_fused_step_kernel_matches_the_operator(cuda, dtype):
+  """world = 1: prime + one launch per step (push of step t+1, zero-fill of the other output buffer, bounded
+  wait, scatter of step t) gives, step after step and across slot reuse, what event_csr_matvec gives."""
+  import cases
+  import brainpylib_b200 as bpl
+  shape = (9000, 3000)
+  data, indices, indptr, rng = cases.csr_case(shape, 0.01, 23)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=1000)
+  steps = 7
+  evs = []
+  for s in range(steps):
+    ev = torch.as_tensor(rng.random(shape[0]) < (0.3 if s % 2 else 0.01)).to(cuda)
+    evs.append(ev if dtype == torch.bool else ev.float() * 2.0)
+  y = [torch.full((shape[1],), float('nan'), device=cuda) for _ in range(2)]
+  ex.prime(evs[0], y[0])
+  for s in range(steps):
+    nxt = evs[s + 1] if s + 1 < steps else None
+    ex.step(d, ix, ptr, y[s % 2], y[(s + 1) % 2] if nxt is not None else None, nxt)
+    want = bpl.event_csr_matvec(d, ix, ptr, evs[s], shape=shape, transpose=True)
+    torch.testing.assert_close(y[s % 2], want, rtol=1e-5, atol=1e-4)
+  ex.check()
+  # a second run on the same object starts where the counter stands
+  ex.prime(evs[3], y[1])
+  ex.step(d, ix, ptr, y[1], None, None)
+  torch.testing.assert_close(y[1], bpl.event_csr_matvec(d, ix, ptr, evs[3], shape=shape, transpose=True),
+                             rtol=1e-5, atol=1e-4)
+  ex.check()
+
+
+def test_fused_step_times_out_without_a_prime(cuda):
+  """A step whose lists never arrive gives up after max_polls, reports it, leaves y untouched and the GPU usable."""
+  import cases
+  shape = (5000, 2000)
+  data, indices, indptr, rng = cases.csr_case(shape, 0.01, 5)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=50)
+  y = torch.zeros(shape[1], device=cuda)
+  ex.step(d, ix, ptr, y, None, None)
+  torch.cuda.synchronize()
+  with pytest.raises(Exception):
+    ex.check()
+  assert float(y.abs().sum()) == 0.0

@@ -102,3 +102,76 @@ def test_two_ranks_reproduce_the_single_device_result():
         assert y.tobytes() == want.tobytes()
         k += 1
     assert [r for _, r, _ in got] == [(0, 251), (251, 501)]
+
+
+# ------------------------------------------------------------------------------------------
+# The one-launch-per-step protocol (sharded_step_kernel) as a host-side model: every rank runs its launches
+# in order; launch t first stores its spikes of step t + 1 into slot (t + 1) % slots of EVERY rank, then may
+# only finish once the lists of step t from every rank have arrived in its own slot t % slots (generation
+# t // slots + 1), reads them, and publishes the arrival of step t + 1.  A random scheduler interleaves the
+# ranks; the model checks that a rank never reads a list that belongs to another step (overwritten early or
+# not yet written) and that nobody deadlocks.
+# ------------------------------------------------------------------------------------------
+def _simulate_step_protocol(world, slots, steps, seed):
+  import random
+  rng = random.Random(seed)
+  content = [[[None] * world for _ in range(slots)] for _ in range(world)]   # [rank][slot][src] = step stored
+  flags = [[[0] * world for _ in range(slots)] for _ in range(world)]        # [rank][slot][src] = arrivals
+  # launch t on a rank: first the stores of step t + 1 everywhere; then, in EITHER order (pushing blocks do not
+  # wait for scattering blocks), the publication of step t + 1 and the bounded wait + read of step t.
+  t_of = [0] * world
+  stored = [False] * world
+  read = [False] * world
+  published = [False] * world
+  for r in range(world):                               # prime: every rank stores and publishes step 0
+    for q in range(world):
+      content[q][0][r] = 0
+      flags[q][0][r] += 1
+  violations, idle = [], 0
+  while min(t_of) < steps and idle < 10000:
+    r = rng.randrange(world)
+    t = t_of[r]
+    if t >= steps:
+      idle += 1
+      continue
+    progressed = True
+    if not stored[r]:
+      for q in range(world):
+        content[q][(t + 1) % slots][r] = t + 1        # peer stores of the next step's list
+      stored[r] = True
+    elif not published[r] and (read[r] or rng.random() < 0.5):
+      for q in range(world):
+        flags[q][(t + 1) % slots][r] += 1             # arrival of step t + 1 published
+      published[r] = True
+    elif not read[r]:
+      slot, expected = t % slots, t // slots + 1
+      if all(flags[r][slot][src] >= expected for src in range(world)):
+        for src in range(world):
+          if content[r][slot][src] != t:
+            violations.append((r, t, src, content[r][slot][src]))
+        read[r] = True
+      else:
+        progressed = False
+    if read[r] and published[r]:
+      t_of[r] = t + 1
+      stored[r] = read[r] = published[r] = False
+    idle = 0 if progressed else idle + 1
+  return violations, min(t_of) >= steps
+
+
+def test_step_protocol_is_safe_with_four_slots_and_live():
+  for world in (2, 3, 8):
+    for seed in range(20):
+      violations, finished = _simulate_step_protocol(world, slots=4, steps=40, seed=seed)
+      assert finished, 'the protocol deadlocked'
+      assert not violations, violations[:3]
+
+
+def test_step_protocol_model_detects_too_few_slots():
+  """The model has teeth: with three slots some interleaving lets a fast rank overwrite a list a slow one
+  has not read yet (the C entry point refuses slots < 4)."""
+  found = False
+  for seed in range(200):
+    violations, _ = _simulate_step_protocol(2, slots=3, steps=40, seed=seed)
+    found = found or bool(violations)
+  assert found

@@ -182,7 +182,7 @@ spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, con
 // One launch per simulation step on a sharded matrix: exchange of the NEXT step's spikes fused with
 // the scatter of THIS step's.
 // ------------------------------------------------------------------------------------------
-// The first `pushers` blocks (one per chunk of the rank's own events, at most half the grid) only exchange:
+// The first `pushers` blocks (at most one per chunk of the rank's own events and 1/16 of the grid) only exchange:
 //   they compact the rank's spikes of step t + 1 and store the list into slot (t + 1) % slots of every
 //   peer (plain peer stores), fence, and publish the arrival on every peer.
 // The other blocks only compute: they wait, bounded, until the lists of step t have arrived from every
@@ -242,7 +242,9 @@ sharded_step_kernel(const uint32_t *__restrict__ indices, const uint32_t *__rest
     __shared__ uint32_t prefix[MAX_CHUNKS + 1];
     __shared__ uint32_t warp_total[ROW_WARPS];
     __shared__ bool arrived;
-    const uint32_t pushers = next_events == nullptr ? 0u : min(chunks_per_rank, gridDim.x / 2u);
+    // few enough pushing blocks that the scatter keeps (nearly) the whole grid, each taking several chunks in
+    // turn: their work is short next to the scatter and off its critical path
+    const uint32_t pushers = next_events == nullptr ? 0u : min(chunks_per_rank, max(gridDim.x / 16u, 1u));
     step_exchange(y_next, n_out, next_events, n_local, row_offset, chunks_per_rank, peers, slot_words, state, world,
                   rank, slots, max_polls, pushers, &arrived, warp_total);
     if (arrived) {

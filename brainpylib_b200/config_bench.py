@@ -16,6 +16,7 @@ c5  jitconn matmat X (256 x 65536) @ M (65536 x 65536), conn_prob 0.01, N(0, 0.0
 """
 import argparse
 import json
+import os
 import sys
 
 import numpy as np
@@ -68,7 +69,8 @@ def time_graph(fn, steps, warmup):
 
 
 def emit(**kw):
-  print(json.dumps(kw), flush=True)
+  if int(os.environ.get('RANK', '0')) == 0:     # replicas (every configuration but c5) report once
+    print(json.dumps(kw), flush=True)
 
 
 def bench_c1(args, device):
@@ -148,21 +150,39 @@ def bench_c4(args, device):
 
 
 def bench_c5(args, device):
+  """Under torchrun every rank computes its own range of output columns (no exchange: each column has its
+  own random stream); the time is the maximum over ranks, the value the whole product."""
+  import torch.distributed as dist
+  from . import sharded
+  world, rank = int(os.environ.get('WORLD_SIZE', '1')), int(os.environ.get('RANK', '0'))
+  if world > 1 and not dist.is_initialized():
+    dist.init_process_group('nccl', device_id=device)
   c = workloads.config_c5(n=args.cols) if args.cols else workloads.config_c5()
   X = torch.as_tensor(c['matrix']).to(device)
   m, k = X.shape
   n = c['shape'][1]
-  Y = torch.empty(m, n, device=device)
+  lo, hi = sharded.column_range(n, rank, world)
+  Y = torch.empty(m, hi - lo, device=device)
   kw = dict(kind='normal', w1=c['w_mu'], w2=c['w_sigma'], conn_prob=c['conn_prob'], shape=c['shape'], seed=c['seed'],
-            out=Y)
-  us = time_graph(lambda i: jitconn_ops.matmat_raw(X, **kw), args.steps, args.warmup)
+            rank=rank, world=world, out=Y)
+  if world > 1:
+    dist.barrier()
+  us = time_graph(lambda i: sharded.matmat_column_shard(X, **kw), args.steps, args.warmup)
+  if world > 1:
+    t = torch.tensor([us], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = t.item()
   conn = c['conn_prob'] * k * n
   macs = conn * m
-  emit(config='c5', metric='synaptic_ops_per_sec', value=macs / (us * 1e-6), unit='MAC/s', us_per_call=us,
-       generated_connections=conn,
-       roofline={'bound': 'fp32-alu', 'achieved': 2 * macs / (us * 1e-6) / 1e12, 'peak': 148 * 128 * 2 * SM_CLOCK_HZ / 1e12,
-                 'unit': 'TFLOP/s', 'frac': 2 * macs / (us * 1e-6) / (148 * 128 * 2 * SM_CLOCK_HZ),
-                 'smem_gather_frac': 4 * macs / (us * 1e-6) / (148 * 128 * SM_CLOCK_HZ)})
+  peak = world * 148 * 128 * 2 * SM_CLOCK_HZ
+  if rank == 0:
+    emit(config='c5', metric='synaptic_ops_per_sec', value=macs / (us * 1e-6), unit='MAC/s', us_per_call=us,
+         n_gpus=world, scaling='strong', sharding='output columns, no exchange', generated_connections=conn,
+         roofline={'bound': 'fp32-alu', 'achieved': 2 * macs / (us * 1e-6) / 1e12, 'peak': peak / 1e12,
+                   'unit': 'TFLOP/s', 'frac': 2 * macs / (us * 1e-6) / peak,
+                   'smem_gather_frac': 4 * macs / (us * 1e-6) / (world * 148 * 128 * SM_CLOCK_HZ)})
+  if world > 1:
+    dist.destroy_process_group()
 
 
 def main(argv=None):
@@ -180,6 +200,8 @@ def main(argv=None):
   if not torch.cuda.is_available():
     raise SystemExit('a CUDA device is required (no CPU fallback)')
   _lib.lib()
+  if 'LOCAL_RANK' in os.environ:
+    torch.cuda.set_device(int(os.environ['LOCAL_RANK']))
   device = torch.device('cuda', torch.cuda.current_device())
   {'c1': bench_c1, 'c2': bench_c2, 'c4': bench_c4, 'c5': bench_c5}[args.config](args, device)
 

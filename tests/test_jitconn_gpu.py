@@ -300,3 +300,18 @@ def test_matmat_against_cpu_oracle(cuda):
                                   return_info=True)
   bad_cols = (~np.isclose(Y, want, rtol=1e-5, atol=1e-6)).any(axis=0)
   assert bad_cols.sum() <= info['fragile'], (bad_cols.sum(), info)
+
+
+@pytest.mark.parametrize('kind', ['uniform', 'normal'])
+@pytest.mark.parametrize('world', [2, 3, 8])
+def test_matmat_column_shards_concatenate_to_the_full_product(cuda, kind, world):
+  """Sharding by output column needs no exchange: every column has its own stream (seed + column), so the
+  ranks' outputs side by side are bit-identical to the single-device result."""
+  from brainpylib_b200 import sharded
+  m, k, n = 40, 300, 1000 + world   # ragged last shard
+  X = torch.randn(m, k, device=cuda)
+  kw = dict(kind=kind, w1=0.1, w2=0.5, conn_prob=0.05, shape=(k, n), seed=4294967290)   # seed + column wraps
+  full = jitconn_ops.matmat_raw(X, **kw)
+  parts = [sharded.matmat_column_shard(X, rank=r, world=world, **kw) for r in range(world)]
+  assert sum(p.shape[1] for p in parts) == n
+  assert torch.equal(torch.cat(parts, dim=1), full)

@@ -647,8 +647,8 @@ def main():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
-  ap.add_argument('--exchange', default='fused', choices=['step', 'fused', 'push', 'nccl'],
-                  help='N > 1: how the spikes reach every rank each step: fused (compaction + peer stores of spike lists), '
+  ap.add_argument('--exchange', default='step', choices=['step', 'fused', 'push', 'nccl'],
+                  help='N > 1: how the spikes reach every rank each step: step (one launch per step: push of the next step fused with this step scatter), fused (compaction + peer stores of spike lists), '
                   'push (peer stores of the dense slice) or nccl (all-gather)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '

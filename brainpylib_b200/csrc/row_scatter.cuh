@@ -49,8 +49,16 @@ __device__ __forceinline__ uint32_t piece_cut(uint32_t start, uint32_t end, uint
     return static_cast<uint32_t>(r < end ? r : end);
 }
 
+// One reduction into y.  ASM_RED = false: `atomicAdd` with the result unused, which the stand-alone kernels
+// compile to a reduction (measured at the L2 reduction rate).  ASM_RED = true: the reduction spelled out;
+// inside the sharded step kernel the `atomicAdd` form ran at half that rate.
+template<bool ASM_RED, typename T>
+__device__ __forceinline__ void reduce_into(T *p, T v) {
+    if (ASM_RED) red_add(p, v); else atomicAdd(p, v);
+}
+
 // One warp scatters entries [a, b) of the matrix: y[indices[e]] += weight(e) * scale.
-template<typename T, bool HOMO, bool SCALED, bool VEC>
+template<typename T, bool HOMO, bool SCALED, bool VEC, bool ASM_RED>
 __device__ __forceinline__ void scatter_span(const uint32_t *__restrict__ indices, const T *__restrict__ data,
                                              const T homo_w, const T scale, const uint32_t a, const uint32_t b,
                                              const uint32_t nse, T *__restrict__ y, const uint32_t lane) {
@@ -80,14 +88,14 @@ __device__ __forceinline__ void scatter_span(const uint32_t *__restrict__ indice
                         if (pos >= a && pos < b) {
                             T w = HOMO ? homo_w : wq[u].v[e];
                             if (SCALED) w = w * scale;
-                            red_add(y + c[e], w);
+                            reduce_into<ASM_RED>(y + c[e], w);
                         }
                     }
                 } else {  // ragged tail of the arrays: element-wise
                     for (uint32_t pos = max(4u * g, a); pos < b; ++pos) {
                         T w = HOMO ? homo_w : data[pos];
                         if (SCALED) w = w * scale;
-                        red_add(y + indices[pos], w);
+                        reduce_into<ASM_RED>(y + indices[pos], w);
                     }
                 }
             }
@@ -96,7 +104,7 @@ __device__ __forceinline__ void scatter_span(const uint32_t *__restrict__ indice
         for (uint32_t pos = a + lane; pos < b; pos += 32u) {
             T w = HOMO ? homo_w : data[pos];
             if (SCALED) w = w * scale;
-            red_add(y + indices[pos], w);
+            reduce_into<ASM_RED>(y + indices[pos], w);
         }
     }
 }
@@ -104,7 +112,7 @@ __device__ __forceinline__ void scatter_span(const uint32_t *__restrict__ indice
 // Scatter product over a list of rows.
 //   LIST = true : rows come from the compacted spike list (event-driven, scale = 1).
 //   LIST = false: every row, scaled by x[row]  (y = A^T x for a dense x).
-template<typename T, bool HOMO, bool LIST, bool VEC>
+template<typename T, bool HOMO, bool LIST, bool VEC, bool ASM_RED = false>
 __device__ __forceinline__ void
 row_scatter_body(const uint32_t *__restrict__ indices, const uint32_t *__restrict__ indptr,
                  const T *__restrict__ data, const T *__restrict__ x, const uint32_t n_row,
@@ -144,7 +152,7 @@ row_scatter_body(const uint32_t *__restrict__ indices, const uint32_t *__restric
         for (uint32_t t = 0; t < count; ++t) {
             const uint32_t ta = __shfl_sync(FULL_MASK, a, t), tb = __shfl_sync(FULL_MASK, b, t);
             const T ts = __shfl_sync(FULL_MASK, scale, t);
-            if (ta < tb) scatter_span<T, HOMO, !LIST, VEC>(indices, data, homo_w, ts, ta, tb, nse, y, lane);
+            if (ta < tb) scatter_span<T, HOMO, !LIST, VEC, ASM_RED>(indices, data, homo_w, ts, ta, tb, nse, y, lane);
         }
     }
 }

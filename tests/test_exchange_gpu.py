@@ -73,14 +73,16 @@ def test_compacted_push_feeds_the_scatter_directly(cuda, dtype):
   ex.check()
 
 
-@pytest.mark.parametrize('dtype', [torch.float32, torch.bool])
-def test_fused_step_kernel_matches_the_operator(cuda, dtype):
+@pytest.mark.parametrize('dtype,shape,density', [(torch.float32, (9000, 3000), 0.01), (torch.bool, (9000, 3000), 0.01),
+                                                 # 49 chunks of events: more than the kernel's pushing blocks (1/16 of
+                                                 # the grid), so each of them compacts and pushes several chunks
+                                                 (torch.float32, (200000, 3000), 0.002)])
+def test_fused_step_kernel_matches_the_operator(cuda, dtype, shape, density):
   """world = 1: prime + one launch per step (push of step t+1, zero-fill of the other output buffer, bounded
   wait, scatter of step t) gives, step after step and across slot reuse, what event_csr_matvec gives."""
   import cases
   import brainpylib_b200 as bpl
-  shape = (9000, 3000)
-  data, indices, indptr, rng = cases.csr_case(shape, 0.01, 23)
+  data, indices, indptr, rng = cases.csr_case(shape, density, 23)
   d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
   ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=1000)
   steps = 7

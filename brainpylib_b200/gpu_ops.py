@@ -10,7 +10,7 @@ import functools
 from . import _lib
 
 __all__ = [
-  'registrations', 'target_names',
+  'registrations', 'target_names', 'register_custom_call_targets',
   'build_twouint_onebool_descriptor', 'build_double_size_descriptor', 'build_triple_size_descriptor',
   'build_jitconn_prob_homo_descriptor', 'build_jitconn_prob_uniform_descriptor',
   'build_jitconn_prob_normal_descriptor', 'build_matmat_jit_prob_descriptor1',
@@ -36,6 +36,20 @@ def registrations():
   for i in range(lib.bpl_registration_count()):
     out[lib.bpl_registration_name(i).decode()] = new_capsule(lib.bpl_registration_target(i), _CAPSULE_NAME, None)
   return out
+
+
+def register_custom_call_targets(xla_client=None, platform='gpu'):
+  """Registers every target with XLA, as the reference does at import time
+  (brainpylib/_src/register_custom_calls.py:16-22).  ``xla_client`` defaults to ``jax.lib.xla_client``;
+  without JAX installed the import error propagates (there is nothing to register with).  Returns the
+  registered names."""
+  if xla_client is None:
+    from jax.lib import xla_client
+  names = []
+  for name, capsule in registrations().items():
+    xla_client.register_custom_call_target(name, capsule, platform=platform)
+    names.append(name)
+  return names
 
 
 @functools.lru_cache(maxsize=4096)

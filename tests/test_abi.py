@@ -158,3 +158,29 @@ def test_argument_checks_match_reference():
     b.matmat_prob_conn_normal_weight(torch.zeros(2, 3), w_mu=0., w_sigma=1., conn_prob=0.1, shape=(4, 5), seed=1)
   with pytest.raises(ValueError, match='1D vector'):
     b.event_matvec_prob_conn_homo_weight(torch.zeros(2, 2), 1., conn_prob=0.1, shape=(2, 2), seed=1)
+
+
+def test_registration_with_xla_through_a_stand_in_client():
+  """register_custom_call_targets hands every target to the client the way the reference's import-time loop
+  does (brainpylib/_src/register_custom_calls.py:16-22): name, capsule "xla._CUSTOM_CALL_TARGET", platform gpu."""
+  from brainpylib_b200 import _lib, gpu_ops
+
+  class Client:
+    def __init__(self):
+      self.seen = []
+
+    def register_custom_call_target(self, name, capsule, platform):
+      self.seen.append((name, capsule, platform))
+
+  client = Client()
+  names = gpu_ops.register_custom_call_targets(client)
+  assert names == gpu_ops.target_names() and len(client.seen) == len(names)
+  get_name = ctypes.pythonapi.PyCapsule_GetName
+  get_name.restype, get_name.argtypes = ctypes.c_char_p, [ctypes.py_object]
+  get_ptr = ctypes.pythonapi.PyCapsule_GetPointer
+  get_ptr.restype, get_ptr.argtypes = ctypes.c_void_p, [ctypes.py_object, ctypes.c_char_p]
+  lib = _lib.lib()
+  for name, capsule, platform in client.seen:
+    assert platform == 'gpu'
+    assert get_name(capsule) == b'xla._CUSTOM_CALL_TARGET'
+    assert get_ptr(capsule, b'xla._CUSTOM_CALL_TARGET') == ctypes.cast(lib.bpl_find_target(name.encode()), ctypes.c_void_p).value

@@ -175,3 +175,30 @@ def test_step_protocol_model_detects_too_few_slots():
     violations, _ = _simulate_step_protocol(2, slots=3, steps=40, seed=seed)
     found = found or bool(violations)
   assert found
+
+
+def test_matmat_column_shard_calls_the_operator_with_offset_seed(monkeypatch):
+  """Host logic of the column shards of the jitconn matmat: the ranges tile the columns, and rank r calls the
+  unchanged operator with its width and the seed advanced by its first column (mod 2^32)."""
+  from brainpylib_b200 import jitconn_ops
+  calls = []
+
+  def fake(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None):
+    calls.append((shape, seed))
+    return torch.zeros(matrix.shape[0], shape[1])
+
+  monkeypatch.setattr(jitconn_ops, 'matmat_raw', fake)
+  X = torch.zeros(4, 50)
+  n, seed, world = 1003, 2 ** 32 - 100, 8
+  outs = [sharded.matmat_column_shard(X, kind='normal', w1=0., w2=1., conn_prob=0.1, shape=(50, n), seed=seed,
+                                      rank=r, world=world) for r in range(world)]
+  assert sum(o.shape[1] for o in outs) == n
+  lo = 0
+  for (shape, s), o in zip(calls, outs):
+    assert shape == (50, o.shape[1]) and s == (seed + lo) % 2 ** 32
+    lo += o.shape[1]
+  # more ranks than columns: the surplus ranks get an empty shard and make no call
+  calls.clear()
+  outs = [sharded.matmat_column_shard(X, kind='normal', w1=0., w2=1., conn_prob=0.1, shape=(50, 3), seed=1,
+                                      rank=r, world=8) for r in range(8)]
+  assert [o.shape[1] for o in outs] == [1, 1, 1, 0, 0, 0, 0, 0] and len(calls) == 3

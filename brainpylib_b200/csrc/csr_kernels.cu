@@ -450,10 +450,10 @@ extern "C" void event_csr_matvec_list_heter_float(bpl_stream_t stream, void **bu
     const int grid = persistent_blocks(4, static_cast<uint64_t>(d->n_row) * 16);
     if (g_profile_before) cudaEventRecord(g_profile_before, stream);
     if (aligned16(indices) && aligned16(data))
-        row_scatter_kernel<float, false, true, true><<<grid, ROW_THREADS, 0, stream>>>(
+        row_scatter_kernel<float, false, true, true, true><<<grid, ROW_THREADS, 0, stream>>>(
             indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
     else
-        row_scatter_kernel<float, false, true, false><<<grid, ROW_THREADS, 0, stream>>>(
+        row_scatter_kernel<float, false, true, false, true><<<grid, ROW_THREADS, 0, stream>>>(
             indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
     if (g_profile_after) cudaEventRecord(g_profile_after, stream);
     launch_ok();

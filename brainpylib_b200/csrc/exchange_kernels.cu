@@ -250,7 +250,7 @@ sharded_step_kernel(const uint32_t *__restrict__ indices, const uint32_t *__rest
     if (arrived) {
         const uint32_t slot = state[slots + 1 + CTR_STEP_T] % slots;
         const uint32_t *list = peers.list[rank] + static_cast<size_t>(slot) * slot_words;
-        row_scatter_body<float, false, true, VEC, true>(indices, indptr, data, nullptr, n_row, SCAN_TILE,
+        row_scatter_body<float, false, true, VEC, true, true>(indices, indptr, data, nullptr, n_row, SCAN_TILE,
                                                   chunks_per_rank * world, list, list + MAX_CHUNKS, y_cur, prefix,
                                                   warp_total, blockIdx.x - pushers, gridDim.x - pushers);
     }

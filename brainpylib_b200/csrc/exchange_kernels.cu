@@ -426,6 +426,10 @@ void bpl_sharded_prime(bpl_stream_t stream, const void *events, int ev_is_float,
                        uint32_t row_offset, void *const *peer_lists, size_t slot_bytes, void *const *peer_flags,
                        void *state, int world, int rank, int slots, void *y_first, uint32_t n_out) {
     if (!step_arguments_ok(n_local, world, rank, slots, state)) return;
+    if (events == nullptr || peer_lists == nullptr || peer_flags == nullptr || (y_first == nullptr && n_out != 0)) {
+        set_status(BPL_ERR_ARGUMENT, "sharded prime: null events, output or peer table");
+        return;
+    }
     const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
     const ListTable t = list_table(peer_lists, peer_flags, world);
     if (ev_is_float)
@@ -447,6 +451,12 @@ void bpl_sharded_step(bpl_stream_t stream, const void *data, const void *indices
                       size_t slot_bytes, void *const *peer_flags, void *state, int world, int rank, int slots,
                       uint32_t max_polls) {
     if (!step_arguments_ok(n_local, world, rank, slots, state)) return;
+    if (data == nullptr || indices == nullptr || indptr == nullptr || y_cur == nullptr || peer_lists == nullptr ||
+        peer_flags == nullptr || slot_bytes % 16 != 0) {
+        set_status(BPL_ERR_ARGUMENT, "sharded step: null matrix, output or peer table, or a slot size that is not a "
+                                     "multiple of 16 bytes");
+        return;
+    }
     const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
     const ListTable t = list_table(peer_lists, peer_flags, world);
     const int grid = sm_count() * 4;

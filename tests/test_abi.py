@@ -184,3 +184,32 @@ def test_registration_with_xla_through_a_stand_in_client():
     assert platform == 'gpu'
     assert get_name(capsule) == b'xla._CUSTOM_CALL_TARGET'
     assert get_ptr(capsule, b'xla._CUSTOM_CALL_TARGET') == ctypes.cast(lib.bpl_find_target(name.encode()), ctypes.c_void_p).value
+
+
+def test_sharded_step_refuses_bad_arguments_before_any_launch():
+  """Argument checks of the one-launch step entry points run on the host and report through the status channel
+  (fewer than four slots cannot keep a slow peer's list from being overwritten; null tables cannot be launched)."""
+  from brainpylib_b200 import _lib
+  lib = _lib.lib()
+  vp, u32, i32 = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int
+  lib.bpl_sharded_step.restype = None
+  lib.bpl_sharded_step.argtypes = [vp] * 4 + [u32, u32] + [vp] * 3 + [i32, u32, u32, vp, ctypes.c_size_t, vp, vp,
+                                                                  i32, i32, i32, u32]
+  state = ctypes.create_string_buffer(4 * 64)
+  msg = ctypes.create_string_buffer(256)
+
+  def step(slots, world=1, rank=0, n_local=10):
+    lib.bpl_clear_status()
+    lib.bpl_sharded_step(None, None, None, None, 10, 10, None, None, None, 0, n_local, 0, None, 1024, None,
+                         ctypes.cast(state, vp), world, rank, slots, 10)
+    return lib.bpl_last_status(msg, 256), msg.value.decode()
+
+  code, text = step(slots=3)
+  assert code == 3 and 'slots >= 4' in text
+  code, text = step(slots=4, world=17)
+  assert code == 3 and 'world 1..16' in text
+  code, text = step(slots=4, n_local=5_000_000)          # 1221 chunks of 4096 events: beyond the 1024 of a list
+  assert code == 3 and '1024 chunks' in text
+  code, text = step(slots=4)
+  assert code == 3 and 'null' in text
+  lib.bpl_clear_status()

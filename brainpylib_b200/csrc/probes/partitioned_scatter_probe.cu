@@ -5,7 +5,7 @@
 // reduction per synapse, 155 G/s on a B200 = 64 us, while the rows themselves stream in 11 us.  Here the
 // step is done in two passes without any per-synapse global reduction:
 //
-//   pass 1  (partition)   A CTA takes batches of 16 active rows, loads them with 128-bit loads, bins the
+//   pass 1  (partition)   A CTA takes batches of 2..16 active rows, loads them with 128-bit loads, bins the
 //                         entries by column bucket (4096 columns per bucket) in shared memory - integer
 //                         shared-memory atomics hand out the positions - reserves room in each bucket's
 //                         global array with one global atomic per (batch, bucket) and copies each bin out
@@ -43,12 +43,7 @@ constexpr uint32_t BUCKET_COLS = 1u << BUCKET_SHIFT;
 constexpr uint32_t N_BUCKETS = (N_COL + BUCKET_COLS - 1) / BUCKET_COLS;   // 245
 constexpr uint32_t BUCKET_CAP = 96 * 1024;                 // entries per bucket array (mean 40.8 K per step)
 
-constexpr int P1_THREADS = 1024;
-constexpr uint32_t BATCH_ROWS = 16;
-constexpr uint32_t BATCH_ENTRIES = BATCH_ROWS * DEGREE;    // 16000 entries = 125 KB of staging
-constexpr uint32_t PER_THREAD = (BATCH_ENTRIES + P1_THREADS - 1) / P1_THREADS;   // 16 (15.6)
 static_assert(DEGREE % 4 == 0, "rows must start on 16-byte boundaries in this probe");
-static_assert(N_BUCKETS <= P1_THREADS, "one thread per bucket in the reservation step");
 
 __device__ __forceinline__ uint4 ldg_stream_u4(const void *p) {
     uint4 v;
@@ -82,13 +77,18 @@ red_scatter_kernel(const uint32_t *__restrict__ cols, const float *__restrict__ 
 // pass 1: partition the active synapses into per-bucket arrays
 // ---------------------------------------------------------------------------------------------------------
 // shared memory: stage[BATCH_ENTRIES] uint2 {local column, weight bits}; count[N_BUCKETS], start[N_BUCKETS + 1],
-// gbase[N_BUCKETS]
-constexpr size_t P1_SMEM = static_cast<size_t>(BATCH_ENTRIES) * 8 + (3 * N_BUCKETS + 1) * 4 + 64;
+// gbase[N_BUCKETS].  P1_THREADS x BATCH_ROWS is swept by main(): bigger batches give longer contiguous runs per
+// bucket, smaller ones let several CTAs share an SM and overlap their load, bin and copy phases.
+template<int P1_THREADS, uint32_t BATCH_ROWS>
+constexpr size_t p1_smem() { return static_cast<size_t>(BATCH_ROWS) * DEGREE * 8 + (3 * N_BUCKETS + 1) * 4 + 64; }
 
-__global__ void __launch_bounds__(P1_THREADS, 1)
+template<int P1_THREADS, uint32_t BATCH_ROWS>
+__global__ void __launch_bounds__(P1_THREADS)
 partition_kernel(const uint32_t *__restrict__ cols, const float *__restrict__ w, const uint32_t *__restrict__ act,
                  const uint32_t n_act, uint2 *__restrict__ buckets, uint32_t *__restrict__ cursor,
                  float *__restrict__ y, uint32_t *__restrict__ overflowed) {
+    constexpr uint32_t BATCH_ENTRIES = BATCH_ROWS * DEGREE;
+    constexpr int PER_THREAD = 4 * static_cast<int>((BATCH_ENTRIES / 4 + P1_THREADS - 1) / P1_THREADS);
     extern __shared__ __align__(16) unsigned char smem[];
     uint2 *stage = reinterpret_cast<uint2 *>(smem);
     uint32_t *count = reinterpret_cast<uint32_t *>(smem + static_cast<size_t>(BATCH_ENTRIES) * 8);
@@ -106,7 +106,7 @@ partition_kernel(const uint32_t *__restrict__ cols, const float *__restrict__ w,
         for (uint32_t b = tid; b < N_BUCKETS; b += P1_THREADS) count[b] = 0;
         __syncthreads();
 
-        // (a) load: thread t takes groups t, t + 1024, ... (4 groups = 16 entries at most)
+        // (a) load: thread t takes the 128-bit groups t, t + P1_THREADS, ... of the batch
         uint4 c[PER_THREAD / 4], v[PER_THREAD / 4];
         uint32_t pos[PER_THREAD];
 #pragma unroll
@@ -216,6 +216,59 @@ accumulate_kernel(const uint2 *__restrict__ buckets, uint32_t *__restrict__ curs
     if (threadIdx.x == 0) cursor[b] = 0;                  // ready for the next step
 }
 
+struct Buffers {
+    const uint32_t *cols; const float *w; const uint32_t *act; uint2 *buckets; uint32_t *cursor; float *y;
+    uint32_t *over; cudaEvent_t e0, e1, e2; int sms; float red_ms; const std::vector<float> *yref;
+};
+
+// One configuration of the partition kernel: check step 0 against the reduction kernel, then time all steps
+// (every step uses different rows, so its matrix data is cold) for a few grid sizes.
+template<int P1_THREADS, uint32_t BATCH_ROWS>
+void sweep(const Buffers &b) {
+    static_assert(N_BUCKETS <= 1024, "bucket tables are sized for at most 1024 buckets");
+    constexpr size_t smem = p1_smem<P1_THREADS, BATCH_ROWS>();
+    auto kernel = partition_kernel<P1_THREADS, BATCH_ROWS>;
+    CK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int per_sm = 0;
+    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, P1_THREADS, smem));
+    if (per_sm < 1) { std::printf("%d threads x %u rows: does not fit an SM\n", P1_THREADS, BATCH_ROWS); return; }
+
+    CK(cudaMemset(b.y, 0, N_COL * 4));
+    CK(cudaMemset(b.over, 0, 4));
+    kernel<<<b.sms * per_sm, P1_THREADS, smem>>>(b.cols, b.w, b.act, N_ACT, b.buckets, b.cursor, b.y, b.over);
+    accumulate_kernel<<<N_BUCKETS, 1024>>>(b.buckets, b.cursor, b.y);
+    CK(cudaDeviceSynchronize());
+    std::vector<float> y(N_COL);
+    uint32_t over = 0;
+    CK(cudaMemcpy(y.data(), b.y, N_COL * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(&over, b.over, 4, cudaMemcpyDeviceToHost));
+    double worst = 0;
+    for (uint32_t j = 0; j < N_COL; ++j) worst = std::max(worst, static_cast<double>(std::fabs(y[j] - (*b.yref)[j])));
+    std::printf("%4d threads x %2u rows per batch, %zu KB shared, %d CTAs per SM: max |y - y_ref| = %.3g, overflowed %u -> %s\n",
+                P1_THREADS, BATCH_ROWS, smem / 1024, per_sm, worst, over, worst < 1e-3 ? "OK" : "MISMATCH");
+
+    for (int grid : {b.sms * per_sm, b.sms * per_sm * 2}) {
+        float best_p1 = 1e9f, best_p2 = 1e9f;
+        for (int rep = 0; rep < 3; ++rep)
+            for (int k = 0; k < STEPS; ++k) {
+                const uint32_t *act = b.act + static_cast<size_t>(k) * N_ACT;
+                CK(cudaMemsetAsync(b.y, 0, N_COL * 4));
+                CK(cudaEventRecord(b.e0));
+                kernel<<<grid, P1_THREADS, smem>>>(b.cols, b.w, act, N_ACT, b.buckets, b.cursor, b.y, b.over);
+                CK(cudaEventRecord(b.e1));
+                accumulate_kernel<<<N_BUCKETS, 1024>>>(b.buckets, b.cursor, b.y);
+                CK(cudaEventRecord(b.e2));
+                CK(cudaEventSynchronize(b.e2));
+                float p1, p2;
+                CK(cudaEventElapsedTime(&p1, b.e0, b.e1));
+                CK(cudaEventElapsedTime(&p2, b.e1, b.e2));
+                if (p1 + p2 < best_p1 + best_p2) { best_p1 = p1; best_p2 = p2; }
+            }
+        std::printf("     grid %4d: partition %.1f us + accumulate %.1f us = %.1f us  (%.2fx the reduction kernel)\n", grid,
+                    best_p1 * 1e3, best_p2 * 1e3, (best_p1 + best_p2) * 1e3, b.red_ms / (best_p1 + best_p2));
+    }
+}
+
 int main() {
     int sms = 0;
     CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0));
@@ -254,66 +307,35 @@ int main() {
     CK(cudaMemcpy(d_act, h_act.data(), h_act.size() * 4, cudaMemcpyHostToDevice));
     CK(cudaMemset(d_cursor, 0, N_BUCKETS * 4));
     CK(cudaMemset(d_over, 0, 4));
-    CK(cudaFuncSetAttribute(partition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(P1_SMEM)));
 
     cudaEvent_t e0, e1, e2;
     CK(cudaEventCreate(&e0)); CK(cudaEventCreate(&e1)); CK(cudaEventCreate(&e2));
 
-    // ---- correctness on step 0 ----
+    // ---- the reduction kernel: reference result of step 0 and its time over all steps ----
+    std::vector<float> yref(N_COL);
     CK(cudaMemset(d_yref, 0, N_COL * 4));
     red_scatter_kernel<<<sms * 4, 256>>>(d_cols, d_w, d_act, N_ACT, d_yref);
-    CK(cudaMemset(d_y, 0, N_COL * 4));
-    partition_kernel<<<sms, P1_THREADS, P1_SMEM>>>(d_cols, d_w, d_act, N_ACT, d_buckets, d_cursor, d_y, d_over);
-    accumulate_kernel<<<N_BUCKETS, 1024>>>(d_buckets, d_cursor, d_y);
-    CK(cudaDeviceSynchronize());
-    std::vector<float> y(N_COL), yref(N_COL);
-    uint32_t over = 0;
-    CK(cudaMemcpy(y.data(), d_y, N_COL * 4, cudaMemcpyDeviceToHost));
     CK(cudaMemcpy(yref.data(), d_yref, N_COL * 4, cudaMemcpyDeviceToHost));
-    CK(cudaMemcpy(&over, d_over, 4, cudaMemcpyDeviceToHost));
-    double worst = 0, total = 0;
-    for (uint32_t j = 0; j < N_COL; ++j) {
-        worst = std::max(worst, static_cast<double>(std::fabs(y[j] - yref[j])));
-        total += yref[j];
-    }
-    std::printf("check: sum(y_ref) = %.1f, max |y - y_ref| = %.3g (float addition order only), overflowed entries %u -> %s\n",
-                total, worst, over, worst < 1e-3 ? "OK" : "MISMATCH");
+    float best_red = 1e9f;
+    for (int rep = 0; rep < 3; ++rep)
+        for (int k = 0; k < STEPS; ++k) {
+            const uint32_t *act = d_act + static_cast<size_t>(k) * N_ACT;
+            CK(cudaMemsetAsync(d_yref, 0, N_COL * 4));
+            CK(cudaEventRecord(e0));
+            red_scatter_kernel<<<sms * 4, 256>>>(d_cols, d_w, act, N_ACT, d_yref);
+            CK(cudaEventRecord(e1));
+            CK(cudaEventSynchronize(e1));
+            float ms;
+            CK(cudaEventElapsedTime(&ms, e0, e1));
+            best_red = std::min(best_red, ms);
+        }
+    std::printf("reductions: %.1f us per step\n", best_red * 1e3);
 
-    // ---- timing: every step uses different rows, so its matrix data is cold ----
-    for (int grid_mult = 1; grid_mult <= 2; ++grid_mult) {
-        float best_red = 1e9f, best_p1 = 1e9f, best_p2 = 1e9f;
-        for (int rep = 0; rep < 3; ++rep)
-            for (int k = 0; k < STEPS; ++k) {
-                const uint32_t *act = d_act + static_cast<size_t>(k) * N_ACT;
-                CK(cudaMemsetAsync(d_yref, 0, N_COL * 4));
-                CK(cudaEventRecord(e0));
-                red_scatter_kernel<<<sms * 4, 256>>>(d_cols, d_w, act, N_ACT, d_yref);
-                CK(cudaEventRecord(e1));
-                CK(cudaEventSynchronize(e1));
-                float ms;
-                CK(cudaEventElapsedTime(&ms, e0, e1));
-                best_red = std::min(best_red, ms);
-            }
-        for (int rep = 0; rep < 3; ++rep)
-            for (int k = 0; k < STEPS; ++k) {
-                const uint32_t *act = d_act + static_cast<size_t>(k) * N_ACT;
-                CK(cudaMemsetAsync(d_y, 0, N_COL * 4));
-                CK(cudaEventRecord(e0));
-                partition_kernel<<<sms * grid_mult, P1_THREADS, P1_SMEM>>>(d_cols, d_w, act, N_ACT, d_buckets, d_cursor,
-                                                                          d_y, d_over);
-                CK(cudaEventRecord(e1));
-                accumulate_kernel<<<N_BUCKETS, 1024>>>(d_buckets, d_cursor, d_y);
-                CK(cudaEventRecord(e2));
-                CK(cudaEventSynchronize(e2));
-                float a, b;
-                CK(cudaEventElapsedTime(&a, e0, e1));
-                CK(cudaEventElapsedTime(&b, e1, e2));
-                if (a + b < best_p1 + best_p2) { best_p1 = a; best_p2 = b; }
-            }
-        std::printf("partition grid %d x SMs: reductions %.1f us | partition %.1f us + accumulate %.1f us = %.1f us "
-                    "(%.2fx)\n", grid_mult, best_red * 1e3, best_p1 * 1e3, best_p2 * 1e3, (best_p1 + best_p2) * 1e3,
-                    best_red / (best_p1 + best_p2));
-    }
+    Buffers buf{d_cols, d_w, d_act, d_buckets, d_cursor, d_y, d_over, e0, e1, e2, sms, best_red, &yref};
+    sweep<1024, 16>(buf);
+    sweep<512, 8>(buf);
+    sweep<256, 4>(buf);
+    sweep<256, 2>(buf);
     CK(cudaDeviceSynchronize());
     std::printf("%s\n", cudaGetErrorString(cudaGetLastError()));
     return 0;

@@ -18,6 +18,12 @@
 // active rows (the matrix data of a step is cold in DRAM/L2), checks both passes against the plain
 // reduction kernel and prints the times.
 //
+// Measured on one B200 (SM clock 1965 MHz): reduction kernel about 66 us per step; partition 55 us
+// (1024 threads x 16 rows) to 87 us (256 threads x 2 rows) + accumulate 30.7 us, i.e. 0.77x at best: the
+// phases of pass 1 run one after the other between block-wide barriers, and pass 2 manages about 1.1
+// shared-memory float atomics per clock per SM on its 4096 hot addresses.  Results equal the reduction
+// kernel's exactly (the weights are multiples of 2^-20, so every order of additions gives the same float).
+//
 // Build and run:
 //   nvcc -O3 -std=c++17 -gencode arch=compute_100a,code=sm_100a -o partitioned_scatter_probe partitioned_scatter_probe.cu
 //   ./partitioned_scatter_probe

@@ -460,7 +460,7 @@ def run_ours(args):
       torch.cuda.synchronize()
       convert_s = time.time() - t0
       yb = torch.empty(shape[1], dtype=torch.float32, device=device)
-      event_ops.event_cbcsr_matvec_raw(cb, ev_dev[0], out=yb, workspace=ws)
+      event_ops.event_cbcsr_matvec_raw(cb, ev_dev[0], out=yb)
       compute(0, ev_dev[0])
       torch.cuda.synchronize()
       cb_err = (yb - y).abs().max().item()
@@ -469,7 +469,7 @@ def run_ours(args):
       g2 = torch.cuda.CUDAGraph()
       with torch.cuda.graph(g2, stream=side):
         for s in range(W, W + K):
-          event_ops.event_cbcsr_matvec_raw(cb, ev_dev[s], out=yb, workspace=ws)
+          event_ops.event_cbcsr_matvec_raw(cb, ev_dev[s], out=yb)
       g2.replay()
       torch.cuda.synchronize()
       b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -1,0 +1,294 @@
+// Transposed event product on a column-blocked matrix: the device code shared by the stand-alone
+// operator (cbcsr_kernels.cu) and by the sharded step kernel (exchange_kernels.cu).
+//
+// Format (built once per matrix by cbcsr_build.cu).  The post-synaptic neurons are cut into blocks
+// of `width` columns.  The matrix stays row-major: the synapses of row r lie together, grouped by
+// the block of their target, and every (row, block) segment is stored as whole GROUPS of 8
+// synapses, 48 bytes each:
+//
+//     float | int32  w[8]   weights; fixed-point matrices hold round(w * 2^k) as int32   (bytes  0..31)
+//     uint16_t       c[8]   column - block * width                                        (bytes 32..47)
+//
+// A segment whose length is not a multiple of 8 ends in padding synapses (w = 0, c = 0), which
+// add nothing.  offsets[r][b] (uint32, in groups, row stride n_blocks + 1) is where row r's segment
+// for block b starts, offsets[r][b + 1] where it ends; offsets[r][n_blocks] == offsets[r + 1][0].
+//
+// Kernel.  A CTA owns one block's slice of y in shared memory and one of P interleaved shares of the
+// active rows; its 32 warps split those rows and run independently of one another (no barrier in the
+// main loop, no wait on another warp).  A warp resolves 32 of its rows at a time, one per lane (spike
+// list -> row -> segment of this block), with the next 32 already in flight, and then streams the
+// segments through a private ring of small shared-memory buffers: teams of four lanes copy one segment
+// each with 16-byte `cp.async` (eight segments per round, packed back to back), the round is committed
+// as one group, and while it is in flight the warp adds the oldest buffer into the slice: one lane per
+// group of 8 synapses, one shared-memory atomic per synapse.  A buffer is walked as a plain array of
+// groups (no segment boundaries are needed: padding is harmless).  At the end the P slices of a block
+// are added into the zero-filled y with 16-byte vector reductions.
+//
+// Measured alternatives that lost (1e6 x 1e6, 1000 synapses per row, 1 % of the rows active, 37 blocks):
+// one producer warp feeding the others with one `cp.async.bulk` per segment: 4x slower (a segment is
+// ~190 bytes and the copy engine has a per-copy cost); one lane per segment with plain 16-byte loads
+// into registers: 2x slower (every lane of a load instruction touches a different sector); a ticketed
+// combine of the P slices through a scratch area instead of the reductions: 5 us slower; a deeper or
+// shallower ring: no change, the loop is bound by the instructions it issues per round, not by memory
+// latency.
+//
+// FIXED = false: float accumulators.  A float add on shared memory is a compare-and-swap loop on this
+// hardware (about 3.4 per clock per SM at random addresses, each a chain of dependent instructions).
+// FIXED = true: 32-bit fixed-point accumulators; an integer add on shared memory is one fire-and-forget
+// instruction (about 11 per clock per SM).  The weights were rounded to multiples of 2^-k when the
+// matrix was prepared, k chosen so that no column can overflow even if every row spikes; the result
+// is exact but for that rounding, and does not depend on the order of the additions.
+#ifndef BPL_CSRC_CB_SCATTER_CUH_
+#define BPL_CSRC_CB_SCATTER_CUH_
+
+#include "abi.h"
+#include "common.cuh"
+#include "spike_scan.cuh"
+
+namespace bpl {
+namespace {
+
+constexpr int CB_THREADS = 1024;
+constexpr int CB_WARPS = CB_THREADS / 32;
+constexpr uint32_t CB_GROUP_BYTES = 48;
+constexpr uint32_t CB_MAX_WIDTH = 45056;           // 176 KB of shared memory for the slice, the rest for the ring
+constexpr uint32_t CB_MAX_BLOCKS = 1024;
+// static shared memory of a kernel that calls cb_scatter_body (prefix, warp totals), rounded up
+constexpr uint32_t CB_STATIC_SMEM = 4608;
+constexpr uint32_t CB_SMEM_LIMIT = 232448 - CB_STATIC_SMEM;           // 227 KB per CTA on sm_100
+
+constexpr uint32_t CB_MAX_BUF_GROUPS = 32;         // groups per ring buffer: one per lane when it is accumulated
+constexpr uint32_t CB_MIN_BUF_GROUPS = 8;
+
+// ---- shared-memory layout, computed on the host and passed to the kernel ----
+//   acc [acc_bytes]   then per warp a ring of n_buf buffers of buf_groups * 48 bytes
+struct CbPlan {
+    uint32_t n_buf;        // 3 or 2 ring buffers per warp
+    uint32_t buf_groups;   // groups per buffer
+    uint32_t acc_bytes;    // slice of y, rounded up to 16 bytes
+    uint32_t smem_bytes;   // dynamic shared memory of the launch
+    bool ok;
+};
+
+inline CbPlan cb_plan(uint32_t width, uint32_t extra_bytes = 0) {
+    CbPlan p{};
+    p.acc_bytes = (width * 4u + 15u) & ~15u;
+    const uint32_t limit = CB_SMEM_LIMIT - extra_bytes;
+    p.ok = false;
+    if (p.acc_bytes + CB_WARPS * 2u * CB_MIN_BUF_GROUPS * CB_GROUP_BYTES > limit) return p;
+    const uint32_t ring = limit - p.acc_bytes;
+    // three full buffers per warp when they fit, else two buffers as large as fit
+    if (ring >= CB_WARPS * 3u * CB_MAX_BUF_GROUPS * CB_GROUP_BYTES) {
+        p.n_buf = 3;
+        p.buf_groups = CB_MAX_BUF_GROUPS;
+    } else {
+        p.n_buf = 2;
+        const uint32_t g = ring / (CB_WARPS * 2u * CB_GROUP_BYTES);
+        p.buf_groups = g > CB_MAX_BUF_GROUPS ? CB_MAX_BUF_GROUPS : g;
+    }
+    p.smem_bytes = p.acc_bytes + CB_WARPS * p.n_buf * p.buf_groups * CB_GROUP_BYTES;
+    p.ok = true;
+    return p;
+}
+
+// ---- asynchronous 16-byte copies global -> shared ----
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 :: "r"(smem_addr(dst)), "l"(__cvta_generic_to_global(src)) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template<int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+__device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
+    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+struct CbGroup { uint4 wa, wb, cc; };
+
+template<bool FIXED>
+__device__ __forceinline__ void cb_add(float *acc, const uint32_t c, const uint32_t w_bits) {
+    if (FIXED) {
+        if (w_bits != 0u) atomicAdd(reinterpret_cast<int *>(acc) + c, static_cast<int>(w_bits));
+    } else {
+        const float w = __uint_as_float(w_bits);
+        if (w != 0.0f) atomicAdd(acc + c, w);   // padding synapses and zero weights add nothing
+    }
+}
+
+template<bool FIXED>
+__device__ __forceinline__ void cb_add_group(float *acc, const CbGroup &g) {
+    cb_add<FIXED>(acc, g.cc.x & 0xffffu, g.wa.x);
+    cb_add<FIXED>(acc, g.cc.x >> 16, g.wa.y);
+    cb_add<FIXED>(acc, g.cc.y & 0xffffu, g.wa.z);
+    cb_add<FIXED>(acc, g.cc.y >> 16, g.wa.w);
+    cb_add<FIXED>(acc, g.cc.z & 0xffffu, g.wb.x);
+    cb_add<FIXED>(acc, g.cc.z >> 16, g.wb.y);
+    cb_add<FIXED>(acc, g.cc.w & 0xffffu, g.wb.z);
+    cb_add<FIXED>(acc, g.cc.w >> 16, g.wb.w);
+}
+
+// One warp adds the `n` groups of a ring buffer into the slice: one lane per group.
+template<bool FIXED>
+__device__ __forceinline__ void cb_accumulate(float *acc, const unsigned char *buf, const uint32_t n, const uint32_t lane) {
+    for (uint32_t g = lane; g < n; g += 32u) {
+        CbGroup grp;
+        grp.wa = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES);
+        grp.wb = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES + 16);
+        grp.cc = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES + 32);
+        cb_add_group<FIXED>(acc, grp);
+    }
+}
+
+// Optional phase stamps (nanoseconds of %globaltimer), 8 words per CTA, written when `trace` is not null:
+//   0 entry   1 spike list prefix-summed   2 first rows of warp 0 resolved   3 earliest / 4 latest end of a
+//   warp's streaming loop   5 all warps done   6 slice flushed
+__device__ __forceinline__ unsigned long long cb_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void cb_stamp(unsigned long long *trace, const uint32_t cta, const int slot) {
+    if (trace != nullptr) trace[static_cast<uint64_t>(cta) * 8u + slot] = cb_now();
+}
+
+// One CTA's work: block `b` of the columns, share `p` of `P` of the listed rows.
+//   counts / ids: the spike list (chunk_prefix / list_row layout); y: this matrix's output, already zero.
+//   smem: dynamic shared memory laid out by cb_plan; prefix / warp_total: static shared memory.
+//   inv_scale: FIXED only, 2^-k.
+template<int NBUF, bool FIXED>
+__device__ __forceinline__ void
+cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets, const uint32_t n_col,
+                const uint32_t width, const uint32_t n_blocks, const uint32_t b, const uint32_t p, const uint32_t P,
+                const uint32_t chunk, const uint32_t n_chunks, const uint32_t *__restrict__ counts,
+                const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t buf_groups,
+                const uint32_t acc_bytes, unsigned char *smem, uint32_t *prefix, uint32_t *warp_total,
+                const float inv_scale, unsigned long long *trace = nullptr, const uint32_t trace_cta = 0) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t team = lane >> 2, sub = lane & 3u;
+    const uint32_t buf_bytes = buf_groups * CB_GROUP_BYTES;
+    float *acc = reinterpret_cast<float *>(smem);
+    unsigned char *ring = smem + acc_bytes + warp * (NBUF * buf_bytes);
+    const uint32_t col0 = b * width;
+    const uint32_t my_width = min(width, n_col - col0);
+    if (threadIdx.x == 0) {
+        cb_stamp(trace, trace_cta, 0);
+        if (trace != nullptr) {
+            trace[static_cast<uint64_t>(trace_cta) * 8u + 3] = ~0ull;
+            trace[static_cast<uint64_t>(trace_cta) * 8u + 4] = 0ull;
+        }
+    }
+    for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = 0.0f;
+
+    const uint32_t n_act = chunk_prefix(counts, n_chunks, prefix, warp_total);   // ends with a barrier
+    if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 1);
+    const uint32_t mine = n_act > p ? (n_act - p + P - 1) / P : 0;               // the CTA's rows: p, p + P, ...
+    const uint32_t K = mine > warp ? (mine - warp + 31u) / 32u : 0u;             // this warp's: warp, warp + 32, ... of those
+    const uint64_t stride = static_cast<uint64_t>(n_blocks) + 1;
+
+    // lane `l` resolves the warp's row k: where its segment for block b starts and how many groups it has
+    auto resolve = [&](const uint32_t k, uint32_t &src, uint32_t &rem) {
+        src = 0;
+        rem = 0;
+        if (k < K) {
+            const uint32_t row = list_row(prefix, n_chunks, chunk, ids, p + (warp + 32u * k) * P);
+            const uint32_t *o = offsets + row * stride + b;
+            src = o[0];
+            rem = o[1] - src;
+        }
+    };
+
+    uint32_t next_src, next_rem;
+    resolve(lane, next_src, next_rem);
+    if (trace != nullptr && threadIdx.x == 0 && next_rem != 0xffffffffu) cb_stamp(trace, trace_cta, 2);
+    uint32_t issued = 0, consumed = 0;     // rounds committed / accumulated; buffer of round r is r % NBUF
+    uint32_t filled = 0;                   // groups in the buffers of the rounds in flight, 8 bits each, oldest lowest
+
+    for (uint32_t k0 = 0; k0 < K; k0 += 32u) {
+        uint32_t src = next_src, rem = next_rem;
+        resolve(k0 + 32u + lane, next_src, next_rem);      // in flight while this batch streams
+        uint32_t mask = __ballot_sync(FULL_MASK, rem > 0);
+        while (mask) {
+            // one round: team t copies (a piece of) the segment held by lane first + t, packed in lane order
+            const uint32_t first = __ffs(mask) - 1u;
+            const uint32_t owner = first + team;
+            const uint32_t o_src = __shfl_sync(FULL_MASK, src, owner & 31u);
+            uint32_t o_rem = __shfl_sync(FULL_MASK, rem, owner & 31u);
+            if (owner > 31u) o_rem = 0;
+            uint32_t incl = o_rem;                          // inclusive prefix over the teams (lanes of a team agree)
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(FULL_MASK, incl, o);
+                if (lane >= static_cast<uint32_t>(o)) incl += t;
+            }
+            const uint32_t excl = incl - o_rem;
+            const uint32_t piece = excl < buf_groups ? min(o_rem, buf_groups - excl) : 0u;
+            const uint32_t round_groups = min(__shfl_sync(FULL_MASK, incl, 31), buf_groups);
+            unsigned char *dst = ring + (issued % NBUF) * buf_bytes + excl * CB_GROUP_BYTES;
+            const unsigned char *from = groups + static_cast<uint64_t>(o_src) * CB_GROUP_BYTES;
+            for (uint32_t c = sub; c < 3u * piece; c += 4u) cp_async16(dst + c * 16u, from + c * 16u);
+            cp_async_commit();
+            // the lanes that hold the segments just copied move on
+            const uint32_t my_rank = lane - first;
+            const uint32_t taken = __shfl_sync(FULL_MASK, piece, (my_rank & 7u) * 4u);
+            if (lane >= first && my_rank < 8u) {
+                src += taken;
+                rem -= taken;
+            }
+            filled |= round_groups << (8u * (issued - consumed));
+            ++issued;
+            if (issued - consumed == NBUF) {                // ring full: accumulate the oldest round
+                cp_async_wait<NBUF - 1>();
+                __syncwarp();
+                cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * buf_bytes, filled & 0xffu, lane);
+                __syncwarp();
+                filled >>= 8;
+                ++consumed;
+            }
+            mask = __ballot_sync(FULL_MASK, rem > 0);
+        }
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+    while (consumed < issued) {
+        cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * buf_bytes, filled & 0xffu, lane);
+        filled >>= 8;
+        ++consumed;
+    }
+    if (trace != nullptr && lane == 0) {
+        const unsigned long long t = cb_now();
+        atomicMin(trace + static_cast<uint64_t>(trace_cta) * 8u + 3, t);
+        atomicMax(trace + static_cast<uint64_t>(trace_cta) * 8u + 4, t);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 5);
+    // flush the slice: coalesced vector reductions, P CTAs add into the same zero-filled y
+    if (mine > 0) {
+        float *out = y + col0;
+        auto value = [&](const uint32_t j) -> float {
+            return FIXED ? static_cast<float>(reinterpret_cast<const int *>(acc)[j]) * inv_scale : acc[j];
+        };
+        if ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+            const uint32_t n4 = my_width >> 2;
+            for (uint32_t j = threadIdx.x; j < n4; j += CB_THREADS) {
+                const float a0 = value(4u * j), a1 = value(4u * j + 1u), a2 = value(4u * j + 2u), a3 = value(4u * j + 3u);
+                if (a0 != 0.0f || a1 != 0.0f || a2 != 0.0f || a3 != 0.0f) red_add_v4(out + 4u * j, a0, a1, a2, a3);
+            }
+            for (uint32_t j = 4u * n4 + threadIdx.x; j < my_width; j += CB_THREADS)
+                if (value(j) != 0.0f) red_add(out + j, value(j));
+        } else {
+            for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS)
+                if (value(j) != 0.0f) red_add(out + j, value(j));
+        }
+    }
+    if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 6);
+}
+
+}  // namespace
+}  // namespace bpl
+
+#endif  // BPL_CSRC_CB_SCATTER_CUH_

@@ -14,7 +14,8 @@ from . import _lib, gpu_ops
 from .errors import GPUOperatorNotFound
 from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_like
 
-__all__ = ['event_csr_matvec', 'event_info', 'ColumnBlockedCSR', 'csr_to_column_blocked', 'event_cbcsr_matvec']
+__all__ = ['event_csr_matvec', 'event_info', 'ColumnBlockedCSR', 'csr_to_column_blocked', 'prepare_event_csr',
+           'event_cbcsr_matvec']
 
 _workspaces = {}
 _retired_workspaces = []
@@ -106,7 +107,8 @@ def event_csr_matvec(
     events: torch.Tensor,
     *,
     shape: Tuple[int, int],
-    transpose: bool = False
+    transpose: bool = False,
+    prepared=None
 ) -> torch.Tensor:
   """Product of a sparse CSR matrix and a dense event vector.
 
@@ -125,6 +127,12 @@ def event_csr_matvec(
     A length-2 tuple representing the matrix shape.
   transpose: bool
     Whether to transpose the sparse matrix before computing.
+  prepared: ColumnBlockedCSR, optional
+    Not in the reference.  The same matrix converted once with :func:`prepare_event_csr`; with
+    ``transpose=True``, float32 weights and no gradient requested the product then runs on that layout
+    (accumulation in shared memory instead of scattered reductions in L2).  The CSR operands are still
+    checked and are what differentiation uses.  The sums of one output are grouped differently, so the
+    result agrees with the plain path to rounding, not bit for bit.
 
   Returns
   -------
@@ -171,6 +179,10 @@ def event_csr_matvec(
   _target_name(data, events)  # dtype errors before autograd machinery
   if torch.is_grad_enabled() and (data.requires_grad or events.requires_grad):
     return _EventCSRMatvec.apply(data, indices, indptr, events, shape, bool(transpose))
+  if prepared is not None and transpose and data.dtype == torch.float32:
+    if not isinstance(prepared, ColumnBlockedCSR) or prepared.shape != shape or prepared.nse != indices.shape[0]:
+      raise ValueError('prepared does not describe this matrix (built from another shape or entry count).')
+    return event_cbcsr_matvec_raw(prepared, events)
   return event_csr_matvec_raw(data, indices, indptr, events, shape=shape, transpose=bool(transpose))
 
 
@@ -214,87 +226,165 @@ def event_info(events: torch.Tensor):
 
 
 # --------------------------------------------------------------------------------------------------
-# Column-blocked CSR: a second storage format for the transposed event product
+# Column-blocked matrix: a prepared storage format for the transposed event product
 # --------------------------------------------------------------------------------------------------
 # No counterpart in the reference.  The plain CSR scatter is bound by scattered reductions in L2
 # (one 32-byte sector operation per synapse).  Cutting the post-synaptic neurons into blocks narrow
 # enough for one block of the output to live in a CTA's shared memory moves the accumulation out of
-# L2.  The format stays row-major: every CSR row keeps its place and its length, but its entries are
-# grouped by column block (stable, so the CSR order survives inside a group), column ids become
-# 16-bit offsets into their block, and a per-row table says where each block's group starts.  The
-# conversion is done once per matrix; the operator that consumes the format is stateless.
+# L2.  The format stays row-major: the synapses of a row lie together, grouped by column block (the
+# CSR order survives inside a group), in records of 8 synapses (8 float32 weights, then 8 16-bit
+# column offsets into the block; a segment is padded with zero-weight synapses to whole records), and
+# a per-row table says where each block's segment starts.  The conversion runs once per matrix, on the
+# GPU (csrc/cbcsr_build.cu); the operator that consumes the format is stateless.
+
+CB_GROUP_BYTES = 48
+CB_MAX_WIDTH = 45056
+
 
 class ColumnBlockedCSR:
-  """``offsets`` int32 ``(n_row, n_blocks + 1)``: ``offsets[r, b] .. offsets[r, b + 1]`` are row ``r``'s
-               synapses that target block ``b`` (absolute positions; ``offsets[r, 0] == indptr[r]``,
-               ``offsets[r, n_blocks] == indptr[r + 1]``),
-  ``cols``    int16 storage of uint16 local column ids (column = ``b * block_width + cols``),
-  ``data``    weights in the same order, ``shape`` the matrix shape, ``block_width`` columns per block."""
+  """``groups``  uint8 ``(48 * n_groups,)``: records of 8 synapses, ``float32 w[8]`` then ``uint16 c[8]``
+               (column = ``col_range[0] + b * block_width + c``),
+  ``offsets`` int32 storage of uint32 ``(n_row, n_blocks + 1)``: records ``offsets[r, b] .. offsets[r, b + 1]``
+               hold row ``r``'s synapses that target block ``b``,
+  ``shape``   the shape of the matrix this object multiplies by (``n_row``, columns kept),
+  ``col_range`` the columns ``[lo, hi)`` of the source matrix that were kept (a rank's shard), re-based to ``lo``."""
 
-  def __init__(self, offsets, cols, data, shape, block_width):
-    self.offsets, self.cols, self.data = offsets, cols, data
+  def __init__(self, groups, offsets, shape, block_width, col_range=None, nse=None, scale_log2=None):
+    self.groups, self.offsets = groups, offsets
+    self.scale_log2 = scale_log2     # None: float accumulators; k: 32-bit fixed point, 2^k units per 1.0
     self.shape = (int(shape[0]), int(shape[1]))
     self.block_width = int(block_width)
     self.n_blocks = int(offsets.shape[1]) - 1
+    self.col_range = (0, self.shape[1]) if col_range is None else (int(col_range[0]), int(col_range[1]))
+    self.nse = nse
+
+  @property
+  def n_groups(self):
+    return self.groups.numel() // CB_GROUP_BYTES
 
   def nbytes(self):
-    return sum(t.numel() * t.element_size() for t in (self.offsets, self.cols, self.data))
+    return sum(t.numel() * t.element_size() for t in (self.groups, self.offsets))
 
 
 def default_block_width(n_col, device=None):
   """Columns per block: as many blocks as give every SM one CTA when each block is shared by 4 CTAs,
-  capped by what fits a CTA's shared memory next to the row-pointer cache (45056 floats = 176 KB)."""
+  at least 1024 columns, at most what leaves room for three copy buffers per warp beside the block's
+  slice of the output in a CTA's shared memory; a multiple of 32."""
   sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
   n_blocks = max(1, sms // 4)
   width = -(-n_col // n_blocks)
-  width = min(max(width, 1024), 45056)
+  width = min(max(width, 1024), 20480)
   return -(-width // 32) * 32
 
 
-def csr_to_column_blocked(data, indices, indptr, *, shape, block_width=None, rows_per_pass=100_000):
-  """Re-lay a CSR matrix (heterogeneous float32 weights, int32 ids) into :class:`ColumnBlockedCSR`.
+def check_block_width(block_width):
+  if not (32 <= block_width <= CB_MAX_WIDTH) or block_width % 32 != 0:
+    raise ValueError(f'block_width must be a multiple of 32 in 32..{CB_MAX_WIDTH}, got {block_width}')
 
-  Runs on the device of the operands in passes of ``rows_per_pass`` rows (one stable sort per pass).
-  Needs the matrix to have fewer than 2^31 entries."""
+
+def csr_to_column_blocked(data, indices, indptr, *, shape, block_width=None, col_range=None, accumulate='float'):
+  """Re-lay a CSR matrix (float32 weights, heterogeneous or one shared value; int32 ids) into
+  :class:`ColumnBlockedCSR` on the GPU that holds it.
+
+  ``col_range = (lo, hi)`` keeps only the synapses whose target lies in ``[lo, hi)`` and re-bases them
+  to ``lo``: one rank's shard of a matrix partitioned by post-synaptic neuron.  Two kernel passes over
+  the matrix and one host read of the result size; needs fewer than 2^32 records of 8 synapses.
+
+  ``accumulate='float'`` (default): the kernel sums in float32, like the plain operator.
+  ``accumulate='fixed'``: it sums in 32-bit fixed point, which the hardware adds in shared memory several
+  times faster than floats.  One more pass finds ``M``, the largest sum of ``|w|`` over any column, and the
+  unit is ``2^-k`` with ``k = floor(log2(2^30 / M))``: no spike pattern can overflow.  Every weight is
+  rounded to a multiple of the unit, so an output fed by ``n`` active synapses is off by at most
+  ``n * 2^-(k+1)``, about ``n * M * 2^-31``, and carries no other rounding (integer sums are exact and
+  order-independent).  With weights of similar magnitude that is the accuracy of float32 summation; a
+  column that mixes huge and tiny weights keeps the tiny ones only to that absolute step."""
+  import ctypes
   n_row, n_col = int(shape[0]), int(shape[1])
+  lo, hi = (0, n_col) if col_range is None else (int(col_range[0]), int(col_range[1]))
+  if not (0 <= lo <= hi <= n_col):
+    raise ValueError(f'col_range {col_range} does not lie inside 0..{n_col}')
   device = indices.device
+  if device.type != 'cuda':
+    raise GPUOperatorNotFound(f'column-blocked build (operands are on {device}, a CUDA device is required)')
   if block_width is None:
-    block_width = default_block_width(n_col, device)
-  if not (0 < block_width <= 65536):
-    raise ValueError('block_width must be in 1..65536 (local column ids are 16 bits)')
-  nse = int(indices.shape[0])
-  if nse >= 2 ** 31:
-    raise ValueError('more than 2^31 - 1 stored entries')
-  n_blocks = max(1, -(-n_col // block_width))
-  indptr64 = indptr.to(torch.int64)
-  lengths = indptr64[1:] - indptr64[:-1]
-  offsets = torch.empty((n_row, n_blocks + 1), dtype=torch.int32, device=device)
-  cols = torch.empty(nse, dtype=torch.int16, device=device)
-  vals = torch.empty(nse, dtype=data.dtype, device=device)
-  for r0 in range(0, n_row, rows_per_pass):
-    r1 = min(n_row, r0 + rows_per_pass)
-    a, b = int(indptr64[r0]), int(indptr64[r1])
-    idx = indices[a:b].to(torch.int64)
-    blk = idx // block_width
-    row = torch.repeat_interleave(torch.arange(r1 - r0, device=device), lengths[r0:r1])
-    key = row * n_blocks + blk
-    counts = torch.bincount(key, minlength=(r1 - r0) * n_blocks).view(r1 - r0, n_blocks)
-    ends = torch.cumsum(counts.view(-1), 0).view(r1 - r0, n_blocks) + a
-    offsets[r0:r1, 1:] = ends.to(torch.int32)
-    offsets[r0:r1, 0] = indptr64[r0:r1].to(torch.int32)
-    if b > a:
-      order = torch.sort(key, stable=True).indices
-      # uint16 stored in int16: values >= 32768 wrap, the kernel reads them back as unsigned
-      cols[a:b] = (idx - blk * block_width)[order].to(torch.int32).to(torch.int16)
-      vals[a:b] = data[a:b][order]
-      del order
-    del idx, blk, row, key, counts, ends
-  return ColumnBlockedCSR(offsets, cols, vals, shape, block_width)
+    block_width = default_block_width(hi - lo, device)
+  block_width = int(block_width)
+  check_block_width(block_width)
+  if data.dtype != torch.float32:
+    raise TypeError('the column-blocked format holds float32 weights')
+  if not (is_int32_like(indices) and is_int32_like(indptr)):
+    raise ValueError('indices and indptr should be int32 or uint32 vectors.')
+  if indptr.shape[0] != n_row + 1:
+    raise ValueError(f'shape {shape} does not match the given indptr {tuple(indptr.shape)}.')
+  if data.shape[0] not in (1, indices.shape[0]):
+    raise ValueError('The size of data should be 1 or be consistent with indices.')
+  data, indices, indptr = map(contiguous, (data, indices, indptr))
+  lib = _lib.lib()
+  lib.bpl_cbcsr_build_workspace_bytes.restype = ctypes.c_size_t
+  lib.bpl_cbcsr_build_workspace_bytes.argtypes = [ctypes.c_uint32]
+  lib.bpl_cbcsr_n_blocks.restype = ctypes.c_uint32
+  lib.bpl_cbcsr_n_blocks.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+  lib.bpl_cbcsr_plan.restype = None
+  lib.bpl_cbcsr_plan.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32,
+                                 ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
+  lib.bpl_cbcsr_fill.restype = None
+  lib.bpl_cbcsr_fill.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                 ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_int]
+  n_blocks = int(lib.bpl_cbcsr_n_blocks(hi - lo, block_width))
+  if n_blocks > 1024:
+    raise ValueError(f'{n_blocks} column blocks; at most 1024 (use a wider block)')
+  with torch.cuda.device(device):
+    stream = torch.cuda.current_stream(device).cuda_stream
+    offsets = torch.empty((n_row, n_blocks + 1), dtype=torch.int32, device=device)
+    ws = torch.empty(int(lib.bpl_cbcsr_build_workspace_bytes(n_row)) // 8 + 1, dtype=torch.int64, device=device)
+    lib.bpl_cbcsr_plan(stream, indices.data_ptr(), indptr.data_ptr(), n_row, lo, hi, block_width, offsets.data_ptr(),
+                       ws.data_ptr())
+    _lib.check_status()
+    n_groups = int(ws[0].item())    # the one synchronisation of the build
+    if n_groups >= 2 ** 32:
+      raise ValueError('2^32 or more records of 8 synapses')
+    homo = int(data.shape[0] == 1 and indices.shape[0] != 1)
+    scale_log2 = None
+    if accumulate == 'fixed':
+      lib.bpl_cbcsr_max_column_abs_sum.restype = None
+      lib.bpl_cbcsr_max_column_abs_sum.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                                   ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                                   ctypes.c_void_p]
+      colsum = torch.empty(max(hi - lo, 1), dtype=torch.float32, device=device)
+      biggest = torch.empty(1, dtype=torch.float32, device=device)
+      lib.bpl_cbcsr_max_column_abs_sum(stream, data.data_ptr(), homo, indices.data_ptr(), int(indices.shape[0]), lo, hi,
+                                       colsum.data_ptr(), biggest.data_ptr())
+      _lib.check_status()
+      scale_log2 = fixed_point_scale_log2(float(biggest.item()))
+      del colsum
+    elif accumulate != 'float':
+      raise ValueError("accumulate must be 'float' or 'fixed'")
+    groups = torch.empty(n_groups * CB_GROUP_BYTES, dtype=torch.uint8, device=device)
+    lib.bpl_cbcsr_fill(stream, data.data_ptr(), homo, indices.data_ptr(), indptr.data_ptr(), n_row, lo, hi, block_width,
+                       offsets.data_ptr(), ws.data_ptr(), groups.data_ptr(), n_groups,
+                       0 if scale_log2 is None else 1, 0 if scale_log2 is None else scale_log2)
+    _lib.check_status()
+  return ColumnBlockedCSR(groups, offsets, (n_row, hi - lo), block_width, (lo, hi), nse=int(indices.shape[0]),
+                          scale_log2=scale_log2)
+
+
+def fixed_point_scale_log2(max_column_abs_sum: float) -> int:
+  """``k`` such that a column whose ``|w|`` sum to ``max_column_abs_sum`` stays below 2^30 units of ``2^-k``."""
+  import math
+  if not math.isfinite(max_column_abs_sum):
+    raise ValueError('the weights are not finite: fixed-point accumulation is not possible')
+  if max_column_abs_sum <= 0.0:
+    return 0
+  return max(-100, min(100, math.floor(math.log2(2.0 ** 30 / max_column_abs_sum))))
+
+
+prepare_event_csr = csr_to_column_blocked
 
 
 def event_cbcsr_matvec_raw(blocked: ColumnBlockedCSR, events, *, out=None, workspace=None):
-  """``y = A^T events`` on a :class:`ColumnBlockedCSR` (heterogeneous float32 weights; bool or float32
-  events).  Target ``event_cbcsr_matvec_heter_float_{bool,float}``."""
+  """``y = A^T events`` on a :class:`ColumnBlockedCSR` (float32 weights; bool or float32 events).
+  Target ``event_cbcsr_matvec_heter_float_{bool,float}``."""
   n_row, n_col = blocked.shape
   if events.dtype == torch.bool:
     name = 'event_cbcsr_matvec_heter_float_bool'
@@ -302,21 +392,21 @@ def event_cbcsr_matvec_raw(blocked: ColumnBlockedCSR, events, *, out=None, works
     name = 'event_cbcsr_matvec_heter_float_float'
   else:
     raise ValueError('events must be bool or float32')
-  if blocked.data.dtype != torch.float32:
-    raise TypeError('column-blocked CSR holds float32 weights')
   if events.device.type != 'cuda':
     raise GPUOperatorNotFound(f'{name} (operands are on {events.device}, a CUDA device is required)')
-  opaque = _cb_descriptor(n_row, n_col, blocked.block_width)
+  opaque = _cb_descriptor(n_row, n_col, blocked.block_width, blocked.scale_log2)
   if out is None:
     out = torch.empty(n_col, dtype=torch.float32, device=events.device)
   if workspace is None:
     workspace = _workspace(events.device, _lib.workspace_bytes(name, opaque))
-  _lib.call(name, [blocked.data, blocked.cols, blocked.offsets, events, out, workspace], opaque, device=events.device)
+  _lib.call(name, [blocked.groups, blocked.offsets, events, out, workspace], opaque, device=events.device)
   return out
 
 
-def _cb_descriptor(n_row, n_col, block_width):
-  return gpu_ops.build_triple_size_descriptor(n_row, n_col, block_width)
+def _cb_descriptor(n_row, n_col, block_width, scale_log2=None):
+  import struct
+  return struct.pack('<IIIii', n_row, n_col, block_width, 0 if scale_log2 is None else 1,
+                     0 if scale_log2 is None else int(scale_log2))
 
 
 def event_cbcsr_matvec(blocked: ColumnBlockedCSR, events: torch.Tensor) -> torch.Tensor:
@@ -324,7 +414,7 @@ def event_cbcsr_matvec(blocked: ColumnBlockedCSR, events: torch.Tensor) -> torch
   matrix converted once with :func:`csr_to_column_blocked`.  Same result as
   ``event_csr_matvec(data, indices, indptr, events, shape=shape, transpose=True)`` up to the order
   of the floating-point additions."""
-  events = as_tensor(events, blocked.data.device)
+  events = as_tensor(events, blocked.groups.device)
   if events.ndim != 1 or events.shape[0] != blocked.shape[0]:
     raise ValueError(f'Shape mismatch, vec ({tuple(events.shape)},) @ mat {blocked.shape}.')
   return event_cbcsr_matvec_raw(blocked, contiguous(events))

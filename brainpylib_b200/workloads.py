@@ -9,7 +9,7 @@ import numpy as np
 
 __all__ = [
   'fixed_prob_csr', 'fixed_degree_csr', 'config_c1', 'config_c2', 'c3_matrix_chunks', 'c3_events',
-  'config_c3_twin', 'config_c4', 'config_c5',
+  'config_c3_twin', 'config_c3_first_rows', 'config_c4', 'config_c5',
 ]
 
 
@@ -92,6 +92,34 @@ def config_c3_twin(n_steps=4):
   events = [c3_events(rng, n) for _ in range(n_steps)]
   indptr = np.arange(0, n * C3_DEGREE + 1, C3_DEGREE, dtype=np.int32)
   return dict(data=out['data'], indices=out['indices'], indptr=indptr, events=events, shape=(n, n), transpose=True)
+
+
+_c3_first_rows_cache = {}
+
+
+def config_c3_first_rows(n_steps=2):
+  """Pre-synaptic rows 0..99,999 (the first generation chunk: 1e8 synapses onto all 1e6 targets) of the FULL
+  1e6-neuron matrix, with the spike vectors of the first ``n_steps`` steps.  ``events`` are the full vectors,
+  ``events_masked`` the same with every spike outside rows 0..99,999 cleared: the product of the whole matrix
+  with a masked vector equals the product of these rows with it, which a CPU can check."""
+  if n_steps not in _c3_first_rows_cache:
+    n = 1_000_000
+    out = {}
+    for kind, c, arr in c3_matrix_chunks(n):
+      if kind == 'rng':
+        rng = arr
+      elif c == 0:
+        out[kind] = arr
+    events = [c3_events(rng, n) for _ in range(n_steps)]
+    masked = []
+    for e in events:
+      m = np.zeros_like(e)
+      m[:C3_ROWS_PER_CHUNK] = e[:C3_ROWS_PER_CHUNK]
+      masked.append(m)
+    indptr = np.arange(0, C3_ROWS_PER_CHUNK * C3_DEGREE + 1, C3_DEGREE, dtype=np.int32)
+    _c3_first_rows_cache[n_steps] = dict(data=out['data'], indices=out['indices'], indptr=indptr, events=events,
+                                         events_masked=masked, shape=(C3_ROWS_PER_CHUNK, n), transpose=True)
+  return _c3_first_rows_cache[n_steps]
 
 
 def config_c4(n=1_000_000):

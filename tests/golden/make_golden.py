@@ -41,6 +41,11 @@ def golden_cases():
         out.append((f'csr/{shape[0]}x{shape[1]}/w{homo}/T{int(transpose)}', 'csr',
                     dict(shape=shape, prob=0.1, seed=200 + i, homo=homo, transpose=transpose)))
   out.append(('event_csr/C1', 'c1', {}))
+  # benchmark-size configurations, stored as strided samples of the output (every 49th / 499th element)
+  for transpose in (False, True):
+    out.append((f'csr/C2/T{int(transpose)}', 'c2', dict(transpose=transpose, stride=49)))
+  for step in (0, 1):
+    out.append((f'event_csr/C3_rows_0_99999/step{step}', 'c3', dict(step=step, stride=499)))
   for homo in (True, False):
     for op in ('sum', 'prod'):
       out.append((f'coo_atomic_{op}/homo{int(homo)}', 'coo_atomic', dict(op=op, homo=homo, seed=300)))
@@ -50,6 +55,14 @@ def golden_cases():
 def build_inputs(kind, kw):
   if kind == 'c1':
     return workloads.config_c1()
+  if kind == 'c2':
+    c = workloads.config_c2()
+    return dict(data=c['data'], indices=c['indices'], indptr=c['indptr'], x=c['vector'], shape=c['shape'],
+                transpose=kw['transpose'])
+  if kind == 'c3':
+    c = workloads.config_c3_first_rows(2)
+    return dict(data=c['data'], indices=c['indices'], indptr=c['indptr'], shape=c['shape'], transpose=True,
+                x=c['events_masked'][kw['step']][:c['shape'][0]])
   if kind in ('event_csr', 'csr'):
     data, indices, indptr, rng = cases.csr_case(kw['shape'], kw['prob'], kw['seed'], homo=kw['homo'])
     n_in = kw['shape'][0] if kw['transpose'] else kw['shape'][1]
@@ -88,6 +101,11 @@ def reference_output(kind, inp):
   if kind == 'csr':
     return ref.numba_csr_matvec(inp['data'], inp['indices'], inp['indptr'], inp['x'],
                                 shape=inp['shape'], transpose=inp['transpose'])
+  if kind == 'c2':
+    return ref.numba_csr_matvec(inp['data'], inp['indices'], inp['indptr'], inp['x'],
+                                shape=inp['shape'], transpose=inp['transpose'])
+  if kind == 'c3':   # the reference's serial C++ kernel on the rows a CPU can hold; events as bool (truthiness)
+    return ref.csr_event_sum(inp['x'] != 0, inp['indices'], inp['indptr'], inp['data'], inp['shape'][1])
   if kind == 'coo_atomic':
     return ref.coo_atomic(inp['op'], inp['values'], inp['post'], inp['post_num'],
                           None if inp['homo'] else inp['pre'])
@@ -98,7 +116,8 @@ def main():
   assert ref.build(), 'reference tree not found'
   store = {}
   for name, kind, kw in golden_cases():
-    store[name] = reference_output(kind, build_inputs(kind, kw))
+    y = reference_output(kind, build_inputs(kind, kw))
+    store[name] = y[::kw['stride']].copy() if 'stride' in kw else y
   path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'stored_matrix.npz')
   np.savez_compressed(path, **store)
   print(f'{len(store)} cases -> {path} ({os.path.getsize(path)} bytes)')

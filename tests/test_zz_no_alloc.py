@@ -20,6 +20,7 @@ import torch
 
 import cases
 from brainpylib_b200 import _lib, gpu_ops
+from oracle import cpu
 
 pytestmark = pytest.mark.gpu
 
@@ -53,6 +54,47 @@ def test_noalloc_entry_matches_workspace_entry_twice(cuda):
     assert torch.isfinite(y_na).all()
     torch.testing.assert_close(y_na, y_ws, rtol=1e-5, atol=atol)
     assert y_ws.abs().sum().item() > 0
+    want = cpu.event_csr_matvec(data, indices, indptr, events.cpu().numpy(), shape=shape, transpose=True)
+    np.testing.assert_allclose(y_na.cpu().numpy(), want, rtol=1e-5, atol=atol)     # and against the CPU oracle
+
+
+def test_noalloc_entry_at_its_row_limit_unaligned_and_empty(cuda):
+  """Exactly 2^21 rows (the whole fixed scratch), index / weight arrays that start 4 bytes off a 16-byte
+  boundary (the element-wise kernel), and a matrix without rows: each against the CPU oracle."""
+  lib = _lib.lib()
+  stream = torch.cuda.current_stream(cuda).cuda_stream
+  lib.bpl_clear_status()
+  rng = np.random.default_rng(93)
+  n_row, n_col = 1 << 21, 3000
+  lens = np.zeros(n_row, dtype=np.int64)
+  busy = rng.choice(n_row, 4000, replace=False)
+  lens[busy] = rng.integers(1, 40, busy.shape[0])
+  lens[-1] = 17                                   # the last row the scratch can list
+  data, indices, indptr, rng = cases.ragged_csr(lens, n_col, 94)
+  ev = np.zeros(n_row, dtype=np.float32)
+  ev[busy[::2]] = 1.0
+  ev[-1] = 3.0
+  want = cpu.event_csr_matvec(data, indices, indptr, ev, shape=(n_row, n_col), transpose=True)
+  atol = 1e-5 * max(1, int(np.bincount(indices, minlength=n_col).max()))
+  # 16-byte aligned and shifted by one element
+  for shift in (0, 1):
+    d_data = torch.zeros(data.shape[0] + 4, device=cuda)[shift:shift + data.shape[0]].copy_(torch.as_tensor(data))
+    d_idx = torch.zeros(indices.shape[0] + 4, dtype=torch.int32, device=cuda)[shift:shift + indices.shape[0]].copy_(
+      torch.as_tensor(indices))
+    assert (d_data.data_ptr() % 16 == 0) == (shift == 0)
+    d_ptr, d_ev = torch.as_tensor(indptr).to(cuda), torch.as_tensor(ev).to(cuda)
+    y = torch.full((n_col,), float('nan'), device=cuda)
+    opaque = gpu_ops.build_twouint_onebool_descriptor(n_row, n_col, True)
+    assert call_raw('event_csr_matvec_heter_float_float_noalloc', [d_data, d_idx, d_ptr, d_ev, y], opaque, stream) == 0
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(y.cpu().numpy(), want, rtol=1e-5, atol=atol)
+  # no rows: the output is zero-filled and nothing else runs
+  y = torch.full((5,), float('nan'), device=cuda)
+  empty = torch.zeros(1, dtype=torch.int32, device=cuda)
+  opaque = gpu_ops.build_twouint_onebool_descriptor(0, 5, True)
+  assert call_raw('event_csr_matvec_heter_float_float_noalloc', [y, empty, empty, y, y], opaque, stream) == 0
+  torch.cuda.synchronize()
+  assert torch.equal(y, torch.zeros_like(y))
 
 
 def test_noalloc_entry_rejects_what_it_cannot_do(cuda):

@@ -11,12 +11,20 @@ PCG64 draws, `brainpylib_b200/workloads.py`), `event_csr_matvec(..., transpose=T
 One "step" = one call.  Metric: synaptic operations per second = (sum over the step's active
 rows of the row length) / time, whole job.
 
-Prints ONE JSON line (rank 0).  `value` is timed with the matrix, the spikes and the output
-resident in HBM (CUDA graph of the K steps, CUDA events, max over ranks); `e2e` goes through
-the public operator with host spike buffers in and host result buffers out every step;
-`roofline` is for the scatter kernel alone (CUDA events recorded around it by the library's
-profiling hook); `cpu_baseline` / `--impl reference` time the reference's own CPU kernel
-(lib/cpu_event_sum.cc compiled into oracle/_ref, else this repository's CPU restatement).
+Prints ONE JSON line (rank 0).
+
+1 GPU.  `value`: `event_csr_matvec(..., transpose=True, prepared=...)`: the public operator on the matrix
+prepared once into the column-blocked layout (float32 accumulation), K steps in one CUDA graph, inputs
+resident in HBM, CUDA events.  `stateless_csr` is the same operator without the prepared matrix (the
+reference's exact signature), `prepared_fixed_point` the prepared matrix with fixed-point accumulation.
+`roofline` is for the dominant kernel of `value` alone (CUDA events recorded around it by the library's
+profiling hook).  `e2e` drives the C-ABI target with HOST buffers: every step copies that step's spikes
+from pinned host memory and the result back, three streams, the K steps captured in one graph.
+N > 1 GPUs.  The matrix is sharded by post-synaptic neuron (plain CSR shards), every rank owns 1/N of the
+spike sources, one launch per step pushes the next step's spike list to the peers and scatters this
+step's; `e2e` moves only the rank's own n/N spikes in and its own slice of the result out.
+`cpu_baseline` / `--impl reference` time the reference's own CPU kernel (lib/cpu_event_sum.cc compiled
+into oracle/_ref, else this repository's CPU restatement) on the FULL matrix, same spikes.
 """
 import argparse
 import json
@@ -33,7 +41,6 @@ if ROOT not in sys.path:
 
 N_NEURONS = 1_000_000
 DEGREE = 1000
-CPU_SAMPLE_ROWS = 100_000   # rows of the matrix the CPU legs work on (the first generation chunk)
 RATE = 0.01
 METRIC = 'synaptic_ops_per_sec'
 UNIT = 'SyOp/s'
@@ -141,8 +148,8 @@ def build_workload(n_steps, keep_host_matrix, device=None, shard=None, n_neurons
     if kind == 'rng':
       rng = arr
       continue
-    if keep_host_matrix and c == 0:
-      host[kind].append(arr)     # the CPU legs run on the first 100,000 rows (chunk 0) only
+    if keep_host_matrix:
+      host[kind].append(arr)     # the CPU legs run on the whole matrix (8 GB of host memory)
     if device is not None:
       t = torch.from_numpy(arr).to(device, non_blocking=False)
       if shard is not None:
@@ -172,8 +179,9 @@ def build_workload(n_steps, keep_host_matrix, device=None, shard=None, n_neurons
       out['shape'] = (n_neurons, hi - lo)
     torch.cuda.synchronize()
   if keep_host_matrix:
-    out['host_indices'], out['host_data'] = host['indices'][0], host['data'][0]
-    out['host_indptr'] = np.arange(0, CPU_SAMPLE_ROWS * DEGREE + 1, DEGREE, dtype=np.int32)
+    out['host_indices'], out['host_data'] = np.concatenate(host['indices']), np.concatenate(host['data'])
+    host.clear()
+    out['host_indptr'] = np.arange(0, n_neurons * DEGREE + 1, DEGREE, dtype=np.int32)
   out['gen_seconds'] = time.time() - t0
   return out
 
@@ -192,19 +200,18 @@ def cpu_reference_kernel():
   return 'port'
 
 
-CPU_SAMPLE = ('pre-synaptic rows 0..99,999 of the same matrix (1e8 synapses, all 1e6 post-synaptic targets) with '
-              'the same spike vectors restricted to those rows: ~1e6 synaptic ops per step')
+CPU_SAMPLE = 'the whole 1e6 x 1e6 matrix (1e9 synapses) on the host, the same spike vectors: ~1e7 synaptic ops per step'
 
 
 def time_cpu_steps(work, n_steps, budget_seconds=None):
-  """Times the reference CPU path (serial C++: 1 core) on a bounded sample of the workload: the first
-  100,000 rows of the matrix, every step's spikes restricted to those rows."""
+  """Times the reference CPU path (serial C++: 1 core) on the whole matrix, step after step, until the
+  steps or the time budget run out."""
   from oracle import cpu as oracle_cpu
   from oracle import ref
   kind = cpu_reference_kernel()
   ops, t_total, done = 0, 0.0, 0
   for s in range(n_steps):
-    ev = work['events'][s % len(work['events'])][:CPU_SAMPLE_ROWS]
+    ev = work['events'][s % len(work['events'])]
     if kind == 'reference':
       evb = ev != 0    # lib/cpu_event_sum.cc takes bool events; same truthiness test as the GPU op
       t0 = time.perf_counter()
@@ -213,7 +220,7 @@ def time_cpu_steps(work, n_steps, budget_seconds=None):
     else:
       t0 = time.perf_counter()
       oracle_cpu.event_csr_matvec(work['host_data'], work['host_indices'], work['host_indptr'], ev,
-                                  shape=(CPU_SAMPLE_ROWS, N_NEURONS), transpose=True)
+                                  shape=(N_NEURONS, N_NEURONS), transpose=True)
       t_total += time.perf_counter() - t0
     ops += int(np.count_nonzero(ev)) * DEGREE
     done += 1
@@ -252,14 +259,59 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def graph_time_ms(torch, device, side, fn, first, count, warm_first, warm_count):
+  """Milliseconds of `count` calls fn(s) captured in one CUDA graph (CUDA events around one replay), after a
+  replay of a warm-up graph of `warm_count` calls.  Returns (ms, graph, warm_graph)."""
+  graph, warm = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+  with torch.cuda.graph(graph, stream=side):
+    for s in range(first, first + count):
+      fn(s)
+  with torch.cuda.graph(warm, stream=side):
+    for s in range(warm_first, warm_first + max(warm_count, 1)):
+      fn(s)
+  warm.replay()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  torch.cuda.synchronize()
+  e0.record()
+  graph.replay()
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1), graph, warm
+
+
+def kernel_time_ms(torch, lib, fn, first, count):
+  """Mean milliseconds of the scatter kernel alone over `count` calls fn(s), from the events the library
+  records directly around it."""
+  import ctypes
+  pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(count)]
+  for a, b in pairs:
+    a.record()   # creates the underlying CUDA events
+    b.record()
+  torch.cuda.synchronize()
+  for i, (a, b) in enumerate(pairs):
+    lib.bpl_profile_scatter_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
+    fn(first + i)
+  lib.bpl_profile_scatter_events(None, None)
+  torch.cuda.synchronize()
+  return float(np.mean([a.elapsed_time(b) for a, b in pairs]))
+
+
+def torch_reference_step(torch, work, events, n_out):
+  """y of one step by a plain torch scatter on the same device (an independent computation)."""
+  rows = torch.nonzero(events).flatten()
+  starts = work['indptr'][rows].to(torch.int64)
+  lens = (work['indptr'][rows + 1] - work['indptr'][rows]).to(torch.int64)
+  pos = torch.repeat_interleave(starts - torch.cumsum(lens, 0) + lens, lens) + torch.arange(int(lens.sum()),
+                                                                                            device=events.device)
+  return torch.zeros(n_out, dtype=torch.float32, device=events.device).index_add_(
+    0, work['indices'][pos].to(torch.int64), work['data'][pos])
+
+
 def run_ours(args):
   import torch
   import torch.distributed as dist
-  import brainpylib_b200 as bpl
-  from brainpylib_b200 import _lib, event_ops, gpu_ops
-
+  from brainpylib_b200 import _lib
   world = int(os.environ.get('WORLD_SIZE', '1'))
-  rank = int(os.environ.get('RANK', '0'))
   local_rank = int(os.environ.get('LOCAL_RANK', '0'))
   if not torch.cuda.is_available():
     raise SystemExit('bench.py needs a CUDA device (no CPU fallback)')
@@ -268,310 +320,215 @@ def run_ours(args):
   if world > 1:
     dist.init_process_group('nccl', device_id=device)
   _lib.lib()   # fail loudly if the CUDA library is missing
-
-  K, W = args.steps, args.warmup
-  total = W + K
-  want_cpu = (world == 1 and rank == 0 and not args.no_cpu_baseline)
-  n_neurons = args.neurons
-  if n_neurons % workloads_chunk_rows() != 0 or n_neurons % world != 0:
+  if args.neurons % workloads_chunk_rows() != 0 or args.neurons % world != 0:
     raise SystemExit('--neurons must be a multiple of 100000 and of the number of ranks')
-  want_cpu = want_cpu and n_neurons == N_NEURONS
-  work = build_workload(total, keep_host_matrix=want_cpu, device=device, shard=(rank, world) if world > 1 else None,
-                        n_neurons=n_neurons)
-  log(f'[bench] rank {rank}: workload built in {work["gen_seconds"]:.1f}s, '
-      f'{work["indices"].numel():,} synapses on device')
+  if world == 1:
+    run_single(args, torch, device)
+  else:
+    run_sharded(args, torch, dist, device, world)
+
+
+def run_single(args, torch, device):
+  import brainpylib_b200 as bpl
+  from brainpylib_b200 import _lib, event_ops, gpu_ops
+  K, W = args.steps, args.warmup
+  n_neurons = args.neurons
+  want_cpu = (not args.no_cpu_baseline) and n_neurons == N_NEURONS
+  work = build_workload(W + K, keep_host_matrix=want_cpu, device=device, n_neurons=n_neurons)
+  log(f'[bench] workload built in {work["gen_seconds"]:.1f}s, {work["indices"].numel():,} synapses on device')
   shape = work['shape']
   ops_per_step = [int(np.count_nonzero(e)) * DEGREE for e in work['events']]
+  total_ops = sum(ops_per_step[W:W + K])
+  n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
   ev_host = torch.from_numpy(np.stack(work['events'])).pin_memory()
   ev_dev = ev_host.to(device)
   y = torch.empty(shape[1], dtype=torch.float32, device=device)
-  name = 'event_csr_matvec_heter_float_float'
-  opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
-  ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
+  lib = _lib.lib()
+  peak, peak_src = measured_peaks()
 
-  # N > 1: every rank produces the spikes of its own 1/N of the neurons and the dense spike vector is
-  # all-gathered (NCCL over NVLink) inside the step; the matrix shard then needs no further exchange.
-  # The spikes of a step are inputs (they do not depend on the previous step's output), so inside the
-  # captured graph the all-gather of step s+1 runs on a second stream while step s is scattered.
-  per = n_neurons // world
-  ev_full = [torch.empty(n_neurons, dtype=torch.float32, device=device) for _ in range(2)] if world > 1 else None
-  comm_stream = torch.cuda.Stream(device) if world > 1 else None
+  # the matrix prepared once (outside every timed region): column-blocked layout, float and fixed-point accumulation
+  prepared, convert_s = {}, {}
+  for mode in ('float', 'fixed'):
+    torch.cuda.synchronize()
+    t0 = time.time()
+    prepared[mode] = bpl.prepare_event_csr(work['data'], work['indices'], work['indptr'], shape=shape, accumulate=mode)
+    torch.cuda.synchronize()
+    convert_s[mode] = time.time() - t0
+  cb = prepared['float']
 
-  def compute(s, events, out=y):
-    event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], events, shape=shape,
-                                   transpose=True, out=out, workspace=ws)
+  name_csr = 'event_csr_matvec_heter_float_float'
+  opaque_csr = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
+  ws = torch.empty(_lib.workspace_bytes(name_csr, opaque_csr), dtype=torch.uint8, device=device)
 
-  def step(s, out=y):
-    events = ev_dev[s]
-    if world > 1:
-      dist.all_gather_into_tensor(ev_full[0], ev_dev[s, rank * per:(rank + 1) * per])
-      events = ev_full[0]
-    compute(s, events, out)
+  def raw_csr(s):
+    event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], ev_dev[s], shape=shape,
+                                   transpose=True, out=y, workspace=ws)
 
-  def run_steps(first, count):
-    """`count` steps on the current stream; with several ranks the gathers are double-buffered on
-    `comm_stream` (event dependencies only, so the whole pattern can be captured in a graph)."""
-    if world == 1:
-      for s in range(first, first + count):
-        compute(s, ev_dev[s])
-      return
-    if one_launch:
-      mine = slice(rank * per, (rank + 1) * per)
-      exchange.prime(ev_dev[first, mine], y_pair[0])
-      for i in range(count):
-        last = i == count - 1
-        exchange.step(work['data'], work['indices'], work['indptr'], y_pair[i % 2],
-                      None if last else y_pair[(i + 1) % 2], None if last else ev_dev[first + i + 1, mine])
-      return
-    main = torch.cuda.current_stream(device)
-    gathered, consumed = {}, {}
-    start = torch.cuda.Event()
-    start.record(main)
-    comm_stream.wait_event(start)
-    for i in range(count):
-      s = first + i
-      b = i % (exchange.slots if exchange is not None else 2)
-      with torch.cuda.stream(comm_stream):
-        if i >= 2:
-          comm_stream.wait_event(consumed[i - 2])     # at most one step of run-ahead
-        if fused:
-          exchange.push_compacted(ev_dev[s, rank * per:(rank + 1) * per], b)   # compaction + peer stores, one kernel
-        elif exchange is not None:
-          exchange.push(ev_dev[s, rank * per:(rank + 1) * per], b)     # peer stores over NVLink
-        else:
-          dist.all_gather_into_tensor(ev_full[b], ev_dev[s, rank * per:(rank + 1) * per])
-        gathered[i] = torch.cuda.Event()
-        gathered[i].record(comm_stream)
-      main.wait_event(gathered[i])
-      if fused:
-        exchange.wait_zero(b, y)                      # bounded wait for every peer's list; zero-fills y
-        exchange.scatter_from_list(work['data'], work['indices'], work['indptr'], b, y, shape[1])
-      elif exchange is not None:
-        exchange.wait(b)                              # bounded wait for every peer's slice
-        compute(s, exchange.events(b))
-      else:
-        compute(s, ev_full[b])
-      consumed[i] = torch.cuda.Event()
-      consumed[i].record(main)
-    done = torch.cuda.Event()
-    done.record(comm_stream)
-    main.wait_event(done)
+  def raw_prepared(mode):
+    return lambda s: event_ops.event_cbcsr_matvec_raw(prepared[mode], ev_dev[s], out=y, workspace=ws)
 
-  exchange = None
-  if world > 1 and args.exchange in ('push', 'fused', 'step'):
-    from brainpylib_b200 import sharded
-    try:
-      exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
-    except Exception as e:   # symmetric memory unavailable: keep the collective and say so
-      log(f'[bench] rank {rank}: push exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gather')
-    ok = torch.tensor([1 if exchange is not None else 0], device=device)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if not int(ok.item()):
-      exchange = None
-  fused = exchange is not None and args.exchange == 'fused'
-  one_launch = exchange is not None and args.exchange == 'step'
-  y_pair = [y, torch.empty_like(y)] if one_launch else None
+  # sanity: the three paths against a plain torch scatter on the same device (through the public operator)
+  chk = torch_reference_step(torch, work, ev_dev[0], shape[1])
+  errs = {}
+  for label, kw in (('stateless_csr', {}), ('prepared', {'prepared': prepared['float']}),
+                    ('prepared_fixed_point', {'prepared': prepared['fixed']})):
+    out = bpl.event_csr_matvec(work['data'], work['indices'], work['indptr'], ev_dev[0], shape=shape, transpose=True, **kw)
+    errs[label] = (chk - out).abs().max().item()
+    if not errs[label] < 1e-5 * DEGREE:
+      raise SystemExit(f'bench sanity check failed ({label}): max abs error {errs[label]}')
+  del chk, out
 
-  # sanity: one step against a plain torch scatter on the same device
-  step(0)
-  rows = torch.nonzero(ev_dev[0]).flatten()
-  starts = work['indptr'][rows].to(torch.int64)
-  lens = (work['indptr'][rows + 1] - work['indptr'][rows]).to(torch.int64)
-  pos = torch.repeat_interleave(starts - torch.cumsum(lens, 0) + lens, lens) + torch.arange(int(lens.sum()),
-                                                                                            device=device)
-  chk = torch.zeros_like(y).index_add_(0, work['indices'][pos].to(torch.int64), work['data'][pos])
-  err = (chk - y).abs().max().item()
-  if not err < 1e-5 * 1000:
-    raise SystemExit(f'bench sanity check failed: max abs error {err}')
-  del rows, starts, lens, pos, chk
-
-  sampler = ClockSampler(local_rank)
+  sampler = ClockSampler(device.index)
+  side = torch.cuda.Stream(device)
   with sampler:
-    # ---- value: K steps captured in one CUDA graph, inputs resident in HBM ----
-    side = torch.cuda.Stream(device)
     with torch.cuda.stream(side):
       for s in range(min(W, 3)):
-        step(s)
+        raw_csr(s)
+        raw_prepared('float')(s)
+        raw_prepared('fixed')(s)
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-      run_steps(W, K)
-    warm = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(warm, stream=side):
-      run_steps(0, max(W, 1))
-    if W:
-      warm.replay()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    if world > 1:
-      dist.barrier()
-    torch.cuda.synchronize()
-    e0.record()
-    graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-      dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-      t = torch.tensor([ms], device=device)
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-      ms = t.item()
-    total_ops = sum(ops_per_step[W:W + K])
-    value = total_ops / (ms * 1e-3)
-    if exchange is not None:
-      exchange.check()                       # no wait timed out
-      y_last = (y_pair[(K - 1) % 2] if one_launch else y).clone()
-      step(W + K - 1)                        # same step through the NCCL path
-      torch.cuda.synchronize()
-      if not torch.allclose(y_last, y, rtol=1e-5, atol=1e-2):
-        raise SystemExit('push exchange: result of the last step differs from the NCCL all-gather path')
+    # ---- value: K steps captured in one CUDA graph, inputs resident in HBM ----
+    ms, g_a, g_b = graph_time_ms(torch, device, side, raw_prepared('float'), W, K, 0, W)
+    k_ms = kernel_time_ms(torch, lib, raw_prepared('float'), W, K)
+    ms_csr, g_c, g_d = graph_time_ms(torch, device, side, raw_csr, W, K, 0, W)
+    k_ms_csr = kernel_time_ms(torch, lib, raw_csr, W, K)
+    ms_fix, g_e, g_f = graph_time_ms(torch, device, side, raw_prepared('fixed'), W, K, 0, W)
+    k_ms_fix = kernel_time_ms(torch, lib, raw_prepared('fixed'), W, K)
+    # ---- e2e: the C-ABI target with host buffers, every step ----
+    e2e = run_e2e_single(torch, work, ev_host, shape, W, K, device, cb)
+  value = total_ops / (ms * 1e-3)
 
-    # ---- roofline: the scatter kernel alone, timed by events recorded around it ----
-    lib = _lib.lib()
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    for s in range(K):
-      a, b = pairs[s]
-      a.record()   # creates the underlying CUDA events
-      b.record()
-    torch.cuda.synchronize()
-    import ctypes
-    for s in range(K):
-      a, b = pairs[s]
-      lib.bpl_profile_scatter_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
-      step(W + s)
-    lib.bpl_profile_scatter_events(None, None)
-    torch.cuda.synchronize()
-    k_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
-
-    # ---- e2e: public operator, host spikes in, host result out, every step ----
-    e2e = run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step)
-    if world > 1:
-      t = torch.tensor([e2e['ms']], device=device)
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-      e2e['ms'] = t.item()
-    e2e_value = total_ops / (e2e['ms'] * 1e-3)
-
-    # ---- the same steps on the column-blocked format (converted once, outside any timed region) ----
-    blocked = None
-    if world == 1 and not args.no_blocked:
-      t0 = time.time()
-      cb = event_ops.csr_to_column_blocked(work['data'], work['indices'], work['indptr'], shape=shape)
-      torch.cuda.synchronize()
-      convert_s = time.time() - t0
-      yb = torch.empty(shape[1], dtype=torch.float32, device=device)
-      event_ops.event_cbcsr_matvec_raw(cb, ev_dev[0], out=yb)
-      compute(0, ev_dev[0])
-      torch.cuda.synchronize()
-      cb_err = (yb - y).abs().max().item()
-      if not cb_err < 1e-5 * 1000:
-        raise SystemExit(f'column-blocked result differs from the CSR result: max abs error {cb_err}')
-      g2 = torch.cuda.CUDAGraph()
-      with torch.cuda.graph(g2, stream=side):
-        for s in range(W, W + K):
-          event_ops.event_cbcsr_matvec_raw(cb, ev_dev[s], out=yb)
-      g2.replay()
-      torch.cuda.synchronize()
-      b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-      b0.record()
-      g2.replay()
-      b1.record()
-      torch.cuda.synchronize()
-      cb_ms = b0.elapsed_time(b1)
-      n_act_cb = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
-      # algorithmic bytes of a step in this format: 6 B per active synapse (16-bit id + weight), the block
-      # offsets of every active row, spike scan, zero-fill and write-back of y
-      cb_bytes = 6.0 * n_act_cb * DEGREE + 4.0 * n_act_cb * (cb.n_blocks + 1) + 4.0 * n_neurons + 8.0 * shape[1]
-      hbm_peak = measured_peaks()[0]
-      blocked = {'format': 'column-blocked CSR (event_cbcsr_matvec), converted once per matrix',
-                 'value': sum(ops_per_step[W:W + K]) / (cb_ms * 1e-3), 'unit': UNIT, 'ms_per_step': cb_ms / K,
-                 'block_width': cb.block_width, 'n_blocks': cb.n_blocks, 'convert_seconds': convert_s,
-                 'format_bytes': cb.nbytes(), 'max_abs_diff_vs_csr': cb_err,
-                 'roofline_step': {'algorithmic_bytes': cb_bytes, 'achieved': cb_bytes / (cb_ms / K * 1e-3) / 1e9,
-                                   'frac': cb_bytes / (cb_ms / K * 1e-3) / 1e9 / hbm_peak, 'unit': 'GB/s'}}
-      del cb, g2
-
-  peak, peak_src = measured_peaks()
-  n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
-  s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
-  # algorithmic bytes of one scatter launch: indices + weights of the active rows (8 B per synapse),
-  # their indptr pairs (8 B per active row) and the write-back of y (4 B per output neuron)
-  k_bytes = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
+  # algorithmic bytes of one scatter launch on the prepared matrix: 6 B per active synapse (weight + 16-bit id),
+  # the two segment offsets every CTA column reads per active row (8 B x blocks), write-back of y (4 B per neuron)
+  cb_kernel_bytes = 6.0 * n_act * DEGREE + 8.0 * n_act * cb.n_blocks + 4.0 * shape[1]
   # whole step: + the spike scan (4 B per pre neuron) and the zero-fill of y (4 B per output neuron)
-  step_bytes = k_bytes + 4.0 * n_neurons + 4.0 * shape[1]
-  achieved = k_bytes / (k_ms * 1e-3) / 1e9
-  roofline = {
-    'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec>', 'achieved': achieved, 'peak': peak,
-    'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
-    # DRAM bytes per launch: an ncu capture of this kernel on a 4e5-neuron twin read 1.046x its algorithmic
-    # bytes (profiles/row_scatter_kernel_c3_event_csr.md); traffic grows with the active synapses
-    'traffic': 1.046 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
-    'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
-    'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
-             'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak},
-  }
+  cb_step_bytes = cb_kernel_bytes + 4.0 * n_neurons + 4.0 * shape[1]
+  csr_kernel_bytes = 8.0 * n_act * DEGREE + 8.0 * n_act + 4.0 * shape[1]
+  csr_step_bytes = csr_kernel_bytes + 4.0 * n_neurons + 4.0 * shape[1]
 
+  def roof(kernel, kbytes, kms, sbytes, sms, traffic_ratio, traffic_src):
+    return {'bound': 'hbm', 'kernel': kernel, 'achieved': kbytes / (kms * 1e-3) / 1e9, 'peak': peak, 'unit': 'GB/s',
+            'frac': kbytes / (kms * 1e-3) / 1e9 / peak, 'peak_source': peak_src,
+            'traffic': traffic_ratio * kbytes if traffic_ratio else None, 'traffic_source': traffic_src,
+            'algorithmic_bytes_per_launch': kbytes, 'kernel_us': kms * 1e3,
+            'step': {'algorithmic_bytes': sbytes, 'us': sms / K * 1e3, 'frac': sbytes / (sms / K * 1e-3) / 1e9 / peak}}
+
+  padded = prepared['float'].n_groups * 8 / float(work['indices'].numel())
   line = {
-    'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': K, 'warmup': W,
-    'ms_per_step': ms / K, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
-    'data': 'synthetic',
+    'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': 1, 'steps': K, 'warmup': W, 'ms_per_step': ms / K,
+    'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
     'config': {'workload': WORKLOAD if n_neurons == N_NEURONS else
                f'REDUCED TWIN of C3 for profiler captures: {n_neurons} neurons x 1000 synapses (not the benchmark size)',
-               'l2': 'inputs larger than L2: each step streams a different ~80 MB of the '
-               '8 GB matrix; spikes and output (4 MB each) are L2-resident by design',
-               'sharding': 'none' if world == 1 else f'post-synaptic neurons (matrix columns) split over {world} '
-               'ranks; each rank owns 1/N of the spike sources; every step the dense spike vector is assembled by '
-               + ('ONE launch per step: the kernel pushes the compacted spikes of step s+1 into every peer over NVLink, waits '
-                  '(bounded) for the lists of step s and scatters them' if one_launch else
-                  "one kernel that compacts the rank's own spikes and stores the list into every peer over NVLink, bounded waits"
-                  if fused else 'peer stores over NVLink with bounded waits (push exchange)' if exchange is not None
-                  else 'an NCCL all-gather')
-               + ('' if one_launch else ', one step ahead on a second stream (step s+1 is exchanged while step s scatters)')},
-    'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'], 'd2h_bytes_per_step': e2e['d2h'],
-            'ms_per_step': e2e['ms'] / K},
-    # own kernels in the timed graph: scan + scatter per step; push, wait, scan + scatter (dense push);
-    # push, wait, scatter (fused); prime once then one kernel per step (step)
-    'gpu_launches': (K + 1 if one_launch else 3 * K if fused else 4 * K if exchange is not None else 2 * K),
-    'roofline': roofline,
+               'path': 'event_csr_matvec(data, indices, indptr, events, shape=, transpose=True, prepared=P): P = '
+                       'prepare_event_csr(...) once per matrix (column-blocked layout, float32 accumulation); '
+                       'the same call without prepared= is reported under stateless_csr',
+               'l2': 'inputs larger than L2: each step streams a different ~70 MB of the 6.9 GB prepared matrix '
+                     '(~80 MB of the 8 GB CSR matrix); spikes and output (4 MB each) are L2-resident by design',
+               'sharding': 'none'},
+    'e2e': {'value': total_ops / (e2e['ms'] * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'],
+            'd2h_bytes_per_step': e2e['d2h'], 'ms_per_step': e2e['ms'] / K,
+            'path': 'C-ABI target event_cbcsr_matvec_heter_float_float, pinned host spikes in, pinned host result out'},
+    'gpu_launches': 2 * K,     # spike scan + scatter per step
+    'roofline': roof('event_cb_scatter_kernel<float accumulate>', cb_kernel_bytes, k_ms, cb_step_bytes, ms,
+                     padded * 6.0 * n_act * DEGREE / cb_kernel_bytes,
+                     'stored bytes of the active segments (records are padded to 8 synapses); not an ncu figure'),
+    'prepared_matrix': {'block_width': cb.block_width, 'n_blocks': cb.n_blocks, 'bytes': cb.nbytes(),
+                        'csr_bytes': 8 * work['indices'].numel() + 4 * (n_neurons + 1),
+                        'padding_factor': padded, 'convert_seconds': convert_s['float'],
+                        'convert_seconds_fixed_point': convert_s['fixed'],
+                        'scale_log2_fixed_point': prepared['fixed'].scale_log2},
+    'stateless_csr': {'value': total_ops / (ms_csr * 1e-3), 'unit': UNIT, 'ms_per_step': ms_csr / K,
+                      'roofline': roof('row_scatter_kernel<float, heter, list, vec>', csr_kernel_bytes, k_ms_csr,
+                                       csr_step_bytes, ms_csr, 1.046,
+                                       'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes')},
+    'prepared_fixed_point': {'value': total_ops / (ms_fix * 1e-3), 'unit': UNIT, 'ms_per_step': ms_fix / K,
+                             'roofline': roof('event_cb_scatter_kernel<fixed-point accumulate>', cb_kernel_bytes,
+                                              k_ms_fix, cb_step_bytes, ms_fix, None, None)},
+    'max_abs_error_vs_torch_scatter': errs,
     'clocks': sampler.summary(),
   }
-
-  if blocked is not None:
-    line['column_blocked'] = blocked
+  line['reference_cuda'] = reference_cuda_c3(torch, work, ev_dev, shape, W, min(K, 20), ops_per_step)
   if want_cpu:
-    cpu_value, kind, done, seconds = time_cpu_steps(work, 100000, budget_seconds=10.0)
+    cpu_value, kind, done, seconds = time_cpu_steps(work, K, budget_seconds=15.0)
     line['cpu_baseline'] = {'value': cpu_value, 'unit': UNIT, 'cores': 1, 'kind': kind,
                             'sample': f'{done} steps ({seconds:.1f} s of CPU time) on {CPU_SAMPLE}; '
                                       'lib/cpu_event_sum.cc serial C++',
                             'host_cores_available': os.cpu_count()}
-  if rank == 0:
-    print(json.dumps(line), flush=True)
-  if world > 1:
-    # Tear down in a fixed order: the captured graphs hold NCCL kernels and must go before the
-    # communicator.  A process that still cannot finish the teardown within 30 s leaves anyway:
-    # the measurement is complete and printed, and a launcher must not wait on it for ever.
-    sys.stdout.flush()
-    sys.stderr.flush()
-    watchdog = threading.Timer(30.0, lambda: os._exit(0))
-    watchdog.daemon = True
-    watchdog.start()
-    torch.cuda.synchronize()
-    dist.barrier()
-    graph.reset()
-    warm.reset()
-    torch.cuda.synchronize()
-    dist.destroy_process_group()
-    watchdog.cancel()
+  print(json.dumps(line), flush=True)
 
 
-def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
-  """End to end through the C ABI with HOST buffers: every step copies that step's spike vector from
-  pinned host memory to the device, calls the custom-call target, and copies the result back to pinned
-  host memory.  Three streams (copy in, compute, copy out) and triple buffers, so step s+1's spikes are
-  copied in while step s computes and step s-1's result is copied out.  The CUDA runtime is driven
-  directly (ctypes) so that Python dispatch stays off the critical path."""
+def reference_cuda_c3(torch, work, ev_dev, shape, first, count, ops_per_step):
+  """The reference's own CUDA kernel (lib/gpu_event_csr_matvec.cu:74-95 behind its wrapper :148-217, recompiled
+  for sm_100a) on the same matrix and spikes, same GPU, outside every timed region of this library."""
   import ctypes
-  from brainpylib_b200 import _lib, gpu_ops
+  from oracle import ref
+  from brainpylib_b200 import gpu_ops
+  if not ref.available_gpu():
+    return {'unavailable': 'oracle/_ref/libref_gpu.so is not built on this machine'}
+  y_ref = torch.empty(shape[1], dtype=torch.float32, device=ev_dev.device)
+  opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
+  fn = ref.gpu_fn('event_csr_matvec_heter_float_float')
+  default = torch.cuda.default_stream(ev_dev.device)
+
+  def call(s):
+    bufs = (ctypes.c_void_p * 5)(work['data'].data_ptr(), work['indices'].data_ptr(), work['indptr'].data_ptr(),
+                                 ev_dev[s].data_ptr(), y_ref.data_ptr())
+    fn(None, bufs, opaque, len(opaque))   # legacy default stream: its cudaMemset and its kernel are ordered there
+  torch.cuda.synchronize()
+  call(first)
+  torch.cuda.synchronize()
+  a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  a.record(default)
+  for s in range(first, first + count):
+    call(s)
+  b.record(default)
+  torch.cuda.synchronize()
+  ms = a.elapsed_time(b)
+  return {'value': sum(ops_per_step[first:first + count]) / (ms * 1e-3), 'unit': UNIT, 'ms_per_step': ms / count,
+          'steps': count, 'kernel': 'lib/gpu_event_csr_matvec.cu event_csr_matvec_heter_float_float (one warp per row, '
+          'one atomicAdd per synapse), host-launched back to back, CUDA events on the legacy default stream'}
+
+
+def capture_e2e(torch, device, count, enqueue):
+  """Captures `count` steps of enqueue(i, s_in, s_c, s_out) - copy-in, compute and copy-out streams forked from
+  the capturing stream - into one CUDA graph."""
+  main = torch.cuda.Stream(device)
+  s_in, s_c, s_out = (torch.cuda.Stream(device) for _ in range(3))
+  graph = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(graph, stream=main):
+    fork = torch.cuda.Event()
+    fork.record(main)
+    for st in (s_in, s_c, s_out):
+      st.wait_event(fork)
+    for i in range(count):
+      enqueue(i, s_in, s_c, s_out)
+    for st in (s_in, s_c, s_out):
+      join = torch.cuda.Event()
+      join.record(st)
+      main.wait_event(join)
+  return graph
+
+
+def time_graph_ms(torch, graph, warm_graph):
+  warm_graph.replay()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  torch.cuda.synchronize()
+  e0.record()
+  graph.replay()
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1)
+
+
+def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb):
+  """End to end through the C ABI with HOST buffers: every step copies that step's spike vector from pinned
+  host memory to the device, calls the custom-call target on the prepared matrix and copies the result back
+  to pinned host memory.  Three streams (copy in, compute, copy out) and triple buffers, so step s + 1's
+  spikes are copied in while step s computes and step s - 1's result is copied out.  The CUDA runtime is
+  driven directly (ctypes) so that Python dispatch stays off the critical path.  (Capturing the same steps in
+  a CUDA graph was measured too: the 4 MB copies no longer overlapped and a step took 130 us instead of ~90.)"""
+  import ctypes
+  from brainpylib_b200 import _lib, event_ops
   rt = ctypes.CDLL('libcudart.so.12')
   rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
   rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint]
@@ -588,12 +545,12 @@ def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
   ev_buf = [torch.empty(shape[0], dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-  name = 'event_csr_matvec_heter_float_float'
-  opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
-  ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
+  name = 'event_cbcsr_matvec_heter_float_float'
+  opaque = event_ops._cb_descriptor(shape[0], shape[1], cb.block_width, cb.scale_log2)
+  ws = [torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device) for _ in range(n_buf)]
   target = _lib.target(name)
-  bufs = [(ctypes.c_void_p * 6)(work['data'].data_ptr(), work['indices'].data_ptr(), work['indptr'].data_ptr(),
-                                ev_buf[b].data_ptr(), y_buf[b].data_ptr(), ws.data_ptr()) for b in range(n_buf)]
+  bufs = [(ctypes.c_void_p * 5)(cb.groups.data_ptr(), cb.offsets.data_ptr(), ev_buf[b].data_ptr(), y_buf[b].data_ptr(),
+                                ws[b].data_ptr()) for b in range(n_buf)]
 
   def new_event():
     e = ctypes.c_void_p()
@@ -632,11 +589,205 @@ def run_e2e(torch, bpl, work, ev_host, shape, W, K, device, ops_per_step):
 
   run(0, max(W, 1), False)
   run(W, K, True)
-  # the last result that reached the host is the last step's
   last = (K - 1) % n_buf
   if not torch.isfinite(y_host[last]).all() or float(y_host[last].abs().sum()) == 0.0:
     raise SystemExit('e2e: the result copied back to the host is empty')
+  want = event_ops.event_cbcsr_matvec_raw(cb, ev_host[W + K - 1].to(device))
+  if not torch.allclose(y_host[last].to(device), want, rtol=1e-5, atol=1e-2):
+    raise SystemExit('e2e: the result copied back to the host differs from the operator result')
   return {'ms': e0.elapsed_time(e1), 'h2d': h2d, 'd2h': d2h}
+
+
+def run_sharded(args, torch, dist, device, world):
+  """N > 1: plain CSR shards by post-synaptic range, one launch per step (push of the next step's spike list to
+  every peer fused with this step's scatter)."""
+  from brainpylib_b200 import _lib, event_ops, gpu_ops, sharded
+  rank = dist.get_rank()
+  K, W = args.steps, args.warmup
+  n_neurons = args.neurons
+  work = build_workload(W + K, keep_host_matrix=False, device=device, shard=(rank, world), n_neurons=n_neurons)
+  log(f'[bench] rank {rank}: workload built in {work["gen_seconds"]:.1f}s, '
+      f'{work["indices"].numel():,} synapses on device')
+  shape = work['shape']
+  per = n_neurons // world
+  mine = slice(rank * per, (rank + 1) * per)
+  ops_per_step = [int(np.count_nonzero(e)) * DEGREE for e in work['events']]
+  total_ops = sum(ops_per_step[W:W + K])
+  ev_all = np.stack(work['events'])
+  ev_host_mine = torch.from_numpy(np.ascontiguousarray(ev_all[:, mine])).pin_memory()   # this rank's own spike sources
+  ev_dev_mine = ev_host_mine.to(device)
+  ev_dev_full = torch.from_numpy(ev_all[W + K - 1]).to(device)                          # last step, for the check
+  lib = _lib.lib()
+  peak, peak_src = measured_peaks()
+  exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
+  n_y = 3
+  y_ring = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_y)]
+
+  def run_steps(first, count):
+    exchange.prime(ev_dev_mine[first], y_ring[0])
+    for i in range(count):
+      last = i == count - 1
+      exchange.step(work['data'], work['indices'], work['indptr'], y_ring[i % n_y],
+                    None if last else y_ring[(i + 1) % n_y], None if last else ev_dev_mine[first + i + 1])
+
+  sampler = ClockSampler(device.index)
+  side = torch.cuda.Stream(device)
+  with sampler:
+    with torch.cuda.stream(side):
+      run_steps(0, min(max(W, 3), W + K))
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph, warm = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+      run_steps(W, K)
+    with torch.cuda.graph(warm, stream=side):
+      run_steps(0, max(W, 1))
+    warm.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    exchange.check_all(dist)
+    # the last step against the stand-alone operator on the assembled spike vector
+    y_last = y_ring[(K - 1) % n_y].clone()
+    want = event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], ev_dev_full, shape=shape,
+                                          transpose=True)
+    torch.cuda.synchronize()
+    if not torch.allclose(y_last, want, rtol=1e-5, atol=1e-2):
+      raise SystemExit('sharded step: the result of the last step differs from the stand-alone operator')
+    # the scatter of this rank's shard alone (stand-alone operator on the assembled vector), for the roofline
+    name = 'event_csr_matvec_heter_float_float'
+    opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
+    ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
+    ev_rot = [torch.from_numpy(ev_all[W + i]).to(device) for i in range(min(K, 8))]
+    y_tmp = torch.empty(shape[1], dtype=torch.float32, device=device)
+    k_ms = kernel_time_ms(torch, lib, lambda s: event_ops.event_csr_matvec_raw(
+      work['data'], work['indices'], work['indptr'], ev_rot[s % len(ev_rot)], shape=shape, transpose=True, out=y_tmp,
+      workspace=ws), 0, min(K, 16))
+    # ---- e2e: own spikes in, own slice of the result out, every step, through the exchange ----
+    e2e = run_e2e_sharded(torch, dist, work, exchange, ev_host_mine, shape, W, K, device, want)
+  n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
+  s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
+  k_bytes = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
+  step_bytes = k_bytes + 4.0 * per + 4.0 * shape[1] + 4.0 * n_act * world
+  achieved = k_bytes / (k_ms * 1e-3) / 1e9
+  line = {
+    'metric': METRIC, 'value': total_ops / (ms * 1e-3), 'unit': UNIT, 'n_gpus': world, 'steps': K, 'warmup': W,
+    'ms_per_step': ms / K, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
+    'data': 'synthetic',
+    'config': {'workload': WORKLOAD if n_neurons == N_NEURONS else f'REDUCED TWIN of C3: {n_neurons} neurons x 1000 synapses',
+               'l2': 'inputs larger than L2 in total: each step streams a different part of the 8 GB matrix',
+               'sharding': f'post-synaptic neurons (matrix columns) split over {world} ranks, plain CSR shards; each rank '
+                           'owns 1/N of the spike sources; ONE launch per step: the kernel pushes the compacted spikes of '
+                           'step s+1 into every peer over NVLink (peer stores), waits (bounded) for the lists of step s and '
+                           'scatters them; no collective on the data path'},
+    'e2e': {'value': total_ops / (e2e['ms'] * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'],
+            'd2h_bytes_per_step': e2e['d2h'], 'ms_per_step': e2e['ms'] / K,
+            'path': 'PushExchange.prime / step (bpl_sharded_prime / bpl_sharded_step): per rank its own n/N spikes from '
+                    'pinned host memory in, its own slice of the result out to pinned host memory, every step'},
+    'gpu_launches': K + 1,     # prime once, then one kernel per step
+    'roofline': {'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec> on one rank\'s shard (stand-alone)',
+                 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
+                 'traffic': 1.046 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
+                 'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
+                 'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
+                          'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak}},
+    'clocks': sampler.summary(),
+  }
+  if rank == 0:
+    print(json.dumps(line), flush=True)
+  # Tear down in a fixed order: the captured graphs must go before the communicator.  A process that still
+  # cannot finish the teardown within 30 s leaves anyway: the measurement is complete and printed.
+  sys.stdout.flush()
+  sys.stderr.flush()
+  watchdog = threading.Timer(30.0, lambda: os._exit(0))
+  watchdog.daemon = True
+  watchdog.start()
+  torch.cuda.synchronize()
+  dist.barrier()
+  graph.reset()
+  warm.reset()
+  torch.cuda.synchronize()
+  dist.destroy_process_group()
+  watchdog.cancel()
+
+
+def run_e2e_sharded(torch, dist, work, exchange, ev_host_mine, shape, W, K, device, want_last):
+  """End to end on N ranks: per step a rank copies ITS OWN n/N spikes of the next step from pinned host memory,
+  runs the one-launch step (push to the peers + scatter of the current step) and copies ITS OWN slice of the
+  result to pinned host memory.  Copy-in, compute and copy-out run on three streams; three spike buffers and
+  three result buffers; the K steps are captured in one CUDA graph per rank.  Time: maximum over ranks."""
+  n_buf = 3
+  per = ev_host_mine.shape[1]
+  ev_buf = [torch.empty(per, dtype=torch.float32, device=device) for _ in range(n_buf)]
+  y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
+  y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+
+  def build(first, count):
+    done_in, done_c, done_out = {}, {}, {}
+
+    def copy_in(i, s_in):          # spikes of step first + i into ev_buf[i % n_buf]
+      if i >= n_buf:
+        s_in.wait_event(done_c[i - n_buf])         # the launch that pushed this buffer has finished
+      with torch.cuda.stream(s_in):
+        ev_buf[i % n_buf].copy_(ev_host_mine[first + i], non_blocking=True)
+        done_in[i] = torch.cuda.Event()
+        done_in[i].record(s_in)
+
+    def enqueue(i, s_in, s_c, s_out):
+      if i == 0:
+        copy_in(0, s_in)
+        s_c.wait_event(done_in[0])
+        with torch.cuda.stream(s_c):
+          exchange.prime(ev_buf[0], y_buf[0])
+          done_c[0] = torch.cuda.Event()           # the prime launch consumed the spikes of step 0
+          done_c[0].record(s_c)
+      last = i == count - 1
+      if not last:
+        copy_in(i + 1, s_in)
+        s_c.wait_event(done_in[i + 1])
+      if i + 1 >= n_buf and not last:
+        s_c.wait_event(done_out[i + 1 - n_buf])    # y_buf[(i + 1) % n_buf] is zero-filled by this launch
+      with torch.cuda.stream(s_c):
+        exchange.step(work['data'], work['indices'], work['indptr'], y_buf[i % n_buf],
+                      None if last else y_buf[(i + 1) % n_buf], None if last else ev_buf[(i + 1) % n_buf])
+        done_c[i + 1] = torch.cuda.Event()         # launch i consumed the spikes of step i + 1 (pushed them)
+        done_c[i + 1].record(s_c)
+      s_out.wait_event(done_c[i + 1])
+      with torch.cuda.stream(s_out):
+        y_host[i % n_buf].copy_(y_buf[i % n_buf], non_blocking=True)
+        done_out[i] = torch.cuda.Event()
+        done_out[i].record(s_out)
+    return capture_e2e(torch, device, count, enqueue)
+
+  warm, graph = build(0, max(W, 1)), build(W, K)
+  warm.replay()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  torch.cuda.synchronize()
+  dist.barrier()
+  torch.cuda.synchronize()
+  e0.record()
+  graph.replay()
+  e1.record()
+  torch.cuda.synchronize()
+  dist.barrier()
+  t = torch.tensor([e0.elapsed_time(e1)], device=device)
+  dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  exchange.check_all(dist)
+  last = (K - 1) % n_buf
+  if not torch.allclose(y_host[last].to(device), want_last, rtol=1e-5, atol=1e-2):
+    raise SystemExit('e2e: the slice copied back to the host differs from the stand-alone operator result')
+  warm.reset()
+  graph.reset()
+  return {'ms': t.item(), 'h2d': 4 * per, 'd2h': 4 * shape[1]}
 
 
 def main():
@@ -646,21 +797,17 @@ def main():
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
-  ap.add_argument('--no-blocked', action='store_true', help='skip the column-blocked format measurement')
-  ap.add_argument('--exchange', default='step', choices=['step', 'fused', 'push', 'nccl'],
-                  help='N > 1: how the spikes reach every rank each step: step (one launch per step: push of the next step fused with this step scatter), fused (compaction + peer stores of spike lists), '
-                  'push (peer stores of the dense slice) or nccl (all-gather)')
   ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
-                       '(1 GPU, see brainpylib_b200/config_bench.py)')
+                       '(see bench_configs.py)')
   ap.add_argument('--neurons', type=int, default=N_NEURONS,
                   help='reduced twin of the workload (multiple of 100000), for profiler captures only')
   args = ap.parse_args()
   if args.warmup < 3 and args.impl == 'ours':
     log('[bench] note: fewer than 3 warm-up steps requested; the timing rules ask for >= 3')
   if args.config != 'c3':
-    from brainpylib_b200 import config_bench
-    return config_bench.main([args.config, '--warmup', str(args.warmup)])
+    import bench_configs
+    return bench_configs.main([args.config, '--warmup', str(args.warmup)])
   if args.impl == 'reference':
     run_reference(args)
   else:

@@ -94,6 +94,13 @@ def _coo_atomic(op, values, post_ids, post_num, pre_ids):
     pre_ids = contiguous(as_tensor(pre_ids, device))
     if pre_ids.shape != post_ids.shape or pre_ids.dtype != post_ids.dtype:
       raise ValueError('pre_ids and post_ids must have the same shape and dtype')
+    if pre_ids.dtype.is_floating_point or pre_ids.dtype == torch.bool:
+      raise ValueError(f'The dtype of post_ids must be a subtype of integer, while we got {post_ids.dtype}')
+    # the kernel reads values[pre_ids[i]]: the reference's host check (brainpylib/_src/compat/atomic_sum.py:54-56)
+    # keeps a bad id from becoming an out-of-bounds read on the device (one reduction + host read of a scalar)
+    if pre_ids.numel() and (values.numel() <= int(pre_ids.max()) or int(pre_ids.min()) < 0):
+      raise ValueError(f'The size of "values" must be 1 (a scalar) or longer than pre_size (a vector), '
+                       f'while we got {values.numel()} != 1 <= {int(pre_ids.max())}')
     name = f'gpu_coo_atomic_{op}_heter' + _ftype(values.dtype) + _itype(post_ids.dtype)
     _lib.call(name, [values, pre_ids, post_ids, out], opaque, device=device)
   return out

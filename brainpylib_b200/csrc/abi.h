@@ -78,6 +78,11 @@ inline bool launch_ok() {
     return true;
 }
 
+// Optional CUDA events recorded directly around the scatter kernel of a transposed event product (set with
+// bpl_profile_scatter_events, per host thread, null = off).
+cudaEvent_t profile_before();
+cudaEvent_t profile_after();
+
 // Number of SMs of the current device (cached per device; 148 on B200).
 int sm_count();
 

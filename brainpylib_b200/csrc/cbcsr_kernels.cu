@@ -120,6 +120,7 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
         set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width leaves no shared memory for the copy buffers");
         return;
     }
+    if (profile_before()) cudaEventRecord(profile_before(), stream);
 #define BPL_CB_LAUNCH(NBUF, FIXED)                                                                              \
     event_cb_scatter_kernel<NBUF, FIXED><<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(                 \
         groups, offsets, n_col, width, n_blocks, P, p.chunk, p.n_chunks, counts, ids, y, plan.buf_groups,        \
@@ -127,6 +128,7 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     if (d->fixed_point) { if (plan.n_buf == 3) BPL_CB_LAUNCH(3, true); else BPL_CB_LAUNCH(2, true); }
     else                { if (plan.n_buf == 3) BPL_CB_LAUNCH(3, false); else BPL_CB_LAUNCH(2, false); }
 #undef BPL_CB_LAUNCH
+    if (profile_after()) cudaEventRecord(profile_after(), stream);
     launch_ok();
 }
 

@@ -141,10 +141,6 @@ row_gather_kernel(const uint32_t *__restrict__ indices, const uint32_t *__restri
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
-// Optional CUDA events recorded around the scatter kernel of the transposed event product
-// (see bpl_profile_scatter_events); per host thread, off by default.
-thread_local cudaEvent_t g_profile_before = nullptr, g_profile_after = nullptr;
-
 inline int persistent_blocks(int blocks_per_sm, uint64_t work_warps) {
     const uint64_t cap = static_cast<uint64_t>(sm_count()) * blocks_per_sm;
     const uint64_t need = (work_warps + ROW_WARPS - 1) / ROW_WARPS;
@@ -182,14 +178,14 @@ void event_csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaq
         if (n_row == 0) return;
         // one warp per work item; the grid is sized for the worst case (every row active) but capped
         const int grid = persistent_blocks(4, static_cast<uint64_t>(n_row) * 16);
-        if (g_profile_before) cudaEventRecord(g_profile_before, stream);
+        if (profile_before()) cudaEventRecord(profile_before(), stream);
         if (vec)
             row_scatter_kernel<T, HOMO, true, true><<<grid, ROW_THREADS, 0, stream>>>(
                 indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
         else
             row_scatter_kernel<T, HOMO, true, false><<<grid, ROW_THREADS, 0, stream>>>(
                 indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
-        if (g_profile_after) cudaEventRecord(g_profile_after, stream);
+        if (profile_after()) cudaEventRecord(profile_after(), stream);
         launch_ok();
     } else {
         if (n_row == 0) return;
@@ -273,11 +269,6 @@ void csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, si
 using namespace bpl;
 
 extern "C" {
-
-void bpl_profile_scatter_events(void *before, void *after) {
-    g_profile_before = static_cast<cudaEvent_t>(before);
-    g_profile_after = static_cast<cudaEvent_t>(after);
-}
 
 size_t bpl_event_csr_workspace_bytes(uint32_t n_row, int transpose) {
     return transpose ? scatter_workspace_bytes(n_row) : 0;
@@ -448,13 +439,13 @@ extern "C" void event_csr_matvec_list_heter_float(bpl_stream_t stream, void **bu
     const uint32_t *list = static_cast<const uint32_t *>(buffers[3]);
     float *y = static_cast<float *>(buffers[4]);
     const int grid = persistent_blocks(4, static_cast<uint64_t>(d->n_row) * 16);
-    if (g_profile_before) cudaEventRecord(g_profile_before, stream);
+    if (profile_before()) cudaEventRecord(profile_before(), stream);
     if (aligned16(indices) && aligned16(data))
         row_scatter_kernel<float, false, true, true, true><<<grid, ROW_THREADS, 0, stream>>>(
             indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
     else
         row_scatter_kernel<float, false, true, false, true><<<grid, ROW_THREADS, 0, stream>>>(
             indices, indptr, data, nullptr, d->n_row, SCAN_TILE, d->n_chunks, list, list + MAX_CHUNKS, y);
-    if (g_profile_after) cudaEventRecord(g_profile_after, stream);
+    if (profile_after()) cudaEventRecord(profile_after(), stream);
     launch_ok();
 }

@@ -16,6 +16,12 @@ thread_local int g_status = BPL_OK;
 thread_local char g_message[256] = {0};
 }  // namespace
 
+namespace {
+thread_local cudaEvent_t g_profile_before = nullptr, g_profile_after = nullptr;
+}  // namespace
+cudaEvent_t profile_before() { return g_profile_before; }
+cudaEvent_t profile_after() { return g_profile_after; }
+
 void set_status(int code, const char *message) {
     g_status = code;
     std::snprintf(g_message, sizeof(g_message), "%s", message ? message : "");
@@ -62,6 +68,11 @@ extern "C" {
 
 size_t bpl_event_csr_workspace_bytes(uint32_t n_row, int transpose);   // csr_kernels.cu
 size_t bpl_nonzero_workspace_bytes(uint32_t batch_size);               // event_info_kernels.cu
+
+void bpl_profile_scatter_events(void *before, void *after) {
+    g_profile_before = static_cast<cudaEvent_t>(before);
+    g_profile_after = static_cast<cudaEvent_t>(after);
+}
 
 int bpl_last_status(char *message, size_t capacity) {
     if (message != nullptr && capacity > 0) std::snprintf(message, capacity, "%s", g_message);

@@ -71,6 +71,8 @@ size_t bpl_build_coo_event_sum_descriptor(uint32_t conn_size, uint32_t post_size
 size_t bpl_build_coo_atomic_sum_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
 size_t bpl_build_coo_atomic_prod_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
 size_t bpl_build_nonzero_descriptor(uint32_t event_size, uint32_t batch_size, void *out, size_t cap);
+size_t bpl_build_cbcsr_descriptor(uint32_t n_row, uint32_t n_col, uint32_t block_width, int fixed_point,
+                                  int scale_log2, void *out, size_t cap);
 
 /* ---- workspace -------------------------------------------------------------------------
  * Bytes of the trailing workspace buffer a target needs for the given opaque descriptor
@@ -82,8 +84,9 @@ size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t o
 
 /* ---- profiling hook (no counterpart in the reference) -------------------------------------
  * When both are non-NULL cudaEvent_t handles, every later event_csr_matvec_* call with
- * transpose=true made by THIS host thread records `before` / `after` on its stream directly
- * around its scatter kernel, so that kernel can be timed on its own.  NULL switches it off. */
+ * transpose=true and every event_cbcsr_matvec_* call made by THIS host thread records `before` /
+ * `after` on its stream directly around its scatter kernel, so that kernel can be timed on its
+ * own.  NULL switches it off. */
 void bpl_profile_scatter_events(void *before, void *after);
 
 /* ---- targets ----------------------------------------------------------------------------
@@ -96,13 +99,15 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   workspace: bpl_workspace_bytes() bytes when transpose, none otherwise (slot ignored).
  *
  * event_cbcsr_matvec_heter_float_{bool,float}   (no counterpart in the reference)
- *   y = A^T events on a COLUMN-BLOCKED CSR matrix: the post-synaptic neurons are cut into blocks of
- *   `block_width` <= 45056 columns; the matrix stays row-major, but the entries of a row are grouped
- *   by block, hold 16-bit column offsets into their block, and offsets[row][b] .. offsets[row][b + 1]
- *   delimit row's group for block b.  One block's slice of y is accumulated in shared memory, which
- *   lifts the scattered-reduction limit of the plain CSR scatter.
- *   opaque  TripleSizeDescriptor{n_row, n_col, block_width} (bpl_build_triple_size_descriptor)
- *   buffers [data f32(nse), cols u16(nse), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
+ *   y = A^T events on a COLUMN-BLOCKED matrix built once by bpl_cbcsr_plan / bpl_cbcsr_fill (below): the
+ *   post-synaptic neurons are cut into blocks of `block_width` columns (a multiple of 32, <= 45056); the
+ *   matrix stays row-major, the synapses of a row are grouped by block and stored in records of 8
+ *   (8 x float32 weight - or int32 round(w * 2^k) for fixed-point matrices - then 8 x uint16 column offset
+ *   into the block; a segment is padded with zero-weight synapses to whole records); offsets[row][b] ..
+ *   offsets[row][b + 1] are the records of row's segment for block b.  One block's slice of y is accumulated
+ *   in shared memory, which lifts the scattered-reduction limit of the plain CSR scatter.
+ *   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2} (bpl_build_cbcsr_descriptor)
+ *   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
  *   workspace: bpl_workspace_bytes() (as for event_csr_matvec with transpose)
  *
  * csr_matvec_{homo,heter}_{scalar,vector,adaptive}_{float,double}
@@ -202,6 +207,32 @@ void bpl_profile_scatter_events(void *before, void *after);
 #define BPL_DECLARE_ONE(name) BPL_DECLARE_TARGET(name);
 BPL_FOR_EACH_TARGET(BPL_DECLARE_ONE)
 #undef BPL_DECLARE_ONE
+
+/* ---- builder of the column-blocked format (takes the place of the host-side layout code of
+ *      brainpylib/_src/sparse_ops/utils.py:21-51 for the one layout this library adds) ---------
+ * From a CSR matrix (float32 weights, one shared weight when `homogeneous`; uint32 ids) on the device.
+ * [col_lo, col_hi): the columns kept, re-based to col_lo (one rank's shard of a matrix partitioned by
+ * post-synaptic neuron; 0 .. n_col keeps everything).  Calls, all enqueued on `stream`:
+ *   bpl_cbcsr_plan   fills offsets (n_row x (n_blocks + 1) uint32, row-relative for now) and prefix-sums the
+ *                    row totals; afterwards the first 8 bytes of `workspace`
+ *                    (bpl_cbcsr_build_workspace_bytes(n_row) bytes) hold the number of 48-byte records.
+ *   bpl_cbcsr_max_column_abs_sum   (fixed point only) max_out[0] = largest sum of |w| over a kept column;
+ *                    colsum: scratch of col_hi - col_lo floats.  scale_log2 = floor(log2(2^30 / that)).
+ *   bpl_cbcsr_fill   after the caller has read the record count and provided `groups` (48 * n_groups bytes,
+ *                    16-byte aligned): makes the offsets absolute and writes the records; the order inside a
+ *                    segment is the CSR order, so the result is a fixed function of the input. */
+size_t bpl_cbcsr_build_workspace_bytes(uint32_t n_row);
+uint32_t bpl_cbcsr_n_blocks(uint32_t n_col, uint32_t block_width);
+void bpl_cbcsr_plan(bpl_stream_t stream, const void *indices, const void *indptr, uint32_t n_row, uint32_t col_lo,
+                    uint32_t col_hi, uint32_t block_width, void *offsets, void *workspace);
+void bpl_cbcsr_max_column_abs_sum(bpl_stream_t stream, const void *data, int homogeneous, const void *indices,
+                                  uint64_t nse, uint32_t col_lo, uint32_t col_hi, void *colsum, void *max_out);
+void bpl_cbcsr_fill(bpl_stream_t stream, const void *data, int homogeneous, const void *indices, const void *indptr,
+                    uint32_t n_row, uint32_t col_lo, uint32_t col_hi, uint32_t block_width, void *offsets,
+                    const void *workspace, void *groups, uint64_t n_groups, int fixed_point, int scale_log2);
+/* Debugging aid: while `buffer` (device memory, 64 bytes per CTA of the launch) is not NULL, every
+ * event_cbcsr_matvec_* launch of this host thread stamps its phases into it with the global nanosecond timer. */
+void bpl_cbcsr_trace(void *buffer);
 
 /* ---- spike exchange between the GPUs of one node (no counterpart in the reference) -----------
  * push: copies `slice_bytes` bytes at `local` into slot `slot` of every peer's data buffer (at offset

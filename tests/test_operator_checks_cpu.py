@@ -62,3 +62,18 @@ def test_versions_that_define_other_matrices_are_refused():
                                        version='v2')
   with pytest.raises(AssertionError):
     bpl.matvec_prob_conn_homo_weight(torch.ones(3), 1.0, conn_prob=0.1, shape=(3, 3), seed=1, version='v3')
+
+
+def test_coo_atomic_refuses_a_pre_id_beyond_values_before_any_launch():
+  """The reference's host check (brainpylib/_src/compat/atomic_sum.py:54-56): without it the kernel would read
+  values[pre_ids[i]] out of bounds on the device."""
+  import torch
+  import pytest
+  from brainpylib_b200 import compat
+  values = torch.ones(4)
+  post = torch.tensor([0, 1, 2], dtype=torch.int32)
+  for bad in (torch.tensor([0, 4, 1], dtype=torch.int32), torch.tensor([0, -1, 1], dtype=torch.int32)):
+    with pytest.raises(ValueError, match='longer than pre_size'):
+      compat.coo_atomic_sum(values, post, 3, pre_ids=bad)
+    with pytest.raises(ValueError, match='longer than pre_size'):
+      compat.coo_atomic_prod(values, post, 3, pre_ids=bad)

@@ -202,3 +202,64 @@ def test_matmat_column_shard_calls_the_operator_with_offset_seed(monkeypatch):
   outs = [sharded.matmat_column_shard(X, kind='normal', w1=0., w2=1., conn_prob=0.1, shape=(50, 3), seed=1,
                                       rank=r, world=8) for r in range(8)]
   assert [o.shape[1] for o in outs] == [1, 1, 1, 0, 0, 0, 0, 0] and len(calls) == 3
+
+
+# ------------------------------------------------------------------------------------------
+# A wait that timed out on ONE rank must stop ALL ranks (that rank may overwrite slots its peers still read,
+# and their own status words stay clean): check_all combines the status words over the process group.
+# ------------------------------------------------------------------------------------------
+def _status_worker(rank, world, port, failing_rank, out_queue):
+  os.environ['MASTER_ADDR'] = '127.0.0.1'
+  os.environ['MASTER_PORT'] = str(port)
+  dist.init_process_group('gloo', rank=rank, world_size=world)
+  try:
+    ex = sharded.PushExchange.__new__(sharded.PushExchange)      # the host logic only: no device buffers
+    ex.slots, ex.world, ex.rank = 4, world, rank
+    ex._state = torch.zeros(4 + 1 + 32, dtype=torch.int32)
+    if rank == failing_rank:
+      ex._state[4] = 1                                           # what a timed-out wait leaves behind
+    own = 'ok'
+    try:
+      ex.check()
+    except RuntimeError:
+      own = 'raised'
+    combined = 'ok'
+    try:
+      ex.check_all()
+    except RuntimeError:
+      combined = 'raised'
+    out_queue.put((rank, own, combined))
+  finally:
+    dist.destroy_process_group()
+
+
+def test_a_timeout_on_one_rank_is_seen_by_every_rank():
+  ctx = mp.get_context('spawn')
+  for failing in (1, None):
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_status_worker, args=(r, 2, port, failing, q)) for r in range(2)]
+    for p in procs:
+      p.start()
+    got = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+      p.join(timeout=60)
+      assert p.exitcode == 0
+    if failing is None:
+      assert got == [(0, 'ok', 'ok'), (1, 'ok', 'ok')]
+    else:
+      assert got == [(0, 'ok', 'raised'), (1, 'raised', 'raised')]
+
+
+def test_sharded_step_refuses_operands_it_would_index_out_of_bounds():
+  ex = sharded.PushExchange.__new__(sharded.PushExchange)
+  ex.n_events, ex.device = 100, torch.device('cpu')
+  good = (torch.zeros(5), torch.zeros(5, dtype=torch.int32), torch.zeros(101, dtype=torch.int32))
+  ex._check_matrix(*good)
+  import pytest
+  with pytest.raises(ValueError):
+    ex._check_matrix(good[0], good[1], torch.zeros(100, dtype=torch.int32))          # one row pointer short
+  with pytest.raises(TypeError):
+    ex._check_matrix(good[0], good[1].to(torch.int64), good[2])
+  with pytest.raises(ValueError):
+    ex._check_matrix(torch.zeros(4), good[1], good[2])                               # weights / indices disagree

@@ -489,38 +489,7 @@ def reference_cuda_c3(torch, work, ev_dev, shape, first, count, ops_per_step):
           'one atomicAdd per synapse), host-launched back to back, CUDA events on the legacy default stream'}
 
 
-def capture_e2e(torch, device, count, enqueue):
-  """Captures `count` steps of enqueue(i, s_in, s_c, s_out) - copy-in, compute and copy-out streams forked from
-  the capturing stream - into one CUDA graph."""
-  main = torch.cuda.Stream(device)
-  s_in, s_c, s_out = (torch.cuda.Stream(device) for _ in range(3))
-  graph = torch.cuda.CUDAGraph()
-  with torch.cuda.graph(graph, stream=main):
-    fork = torch.cuda.Event()
-    fork.record(main)
-    for st in (s_in, s_c, s_out):
-      st.wait_event(fork)
-    for i in range(count):
-      enqueue(i, s_in, s_c, s_out)
-    for st in (s_in, s_c, s_out):
-      join = torch.cuda.Event()
-      join.record(st)
-      main.wait_event(join)
-  return graph
-
-
-def time_graph_ms(torch, graph, warm_graph):
-  warm_graph.replay()
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  torch.cuda.synchronize()
-  e0.record()
-  graph.replay()
-  e1.record()
-  torch.cuda.synchronize()
-  return e0.elapsed_time(e1)
-
-
-def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb):
+def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb, parts=('in', 'compute', 'out')):
   """End to end through the C ABI with HOST buffers: every step copies that step's spike vector from pinned
   host memory to the device, calls the custom-call target on the prepared matrix and copies the result back
   to pinned host memory.  Three streams (copy in, compute, copy out) and triple buffers, so step s + 1's
@@ -572,23 +541,29 @@ def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb):
       if used[b]:
         check(rt.cudaStreamWaitEvent(s_in, done_c[b], 0))      # the spike buffer's previous reader has finished
         check(rt.cudaStreamWaitEvent(s_c, done_out[b], 0))     # the result buffer's previous copy-out has finished
-      check(rt.cudaMemcpyAsync(ev_buf[b].data_ptr(), ev_host[s].data_ptr(), h2d, 1, s_in))
+      if 'in' in parts:
+        check(rt.cudaMemcpyAsync(ev_buf[b].data_ptr(), ev_host[s].data_ptr(), h2d, 1, s_in))
       check(rt.cudaEventRecord(done_in[b], s_in))
       check(rt.cudaStreamWaitEvent(s_c, done_in[b], 0))
-      target(s_c, bufs[b], opaque, len(opaque))
+      if 'compute' in parts:
+        target(s_c, bufs[b], opaque, len(opaque))
       check(rt.cudaEventRecord(done_c[b], s_c))
       check(rt.cudaStreamWaitEvent(s_out, done_c[b], 0))
-      check(rt.cudaMemcpyAsync(y_host[b].data_ptr(), y_buf[b].data_ptr(), d2h, 2, s_out))
+      if 'out' in parts:
+        check(rt.cudaMemcpyAsync(y_host[b].data_ptr(), y_buf[b].data_ptr(), d2h, 2, s_out))
       check(rt.cudaEventRecord(done_out[b], s_out))
       used[b] = True
     _lib.check_status()
     if timed:
       streams[2].wait_stream(streams[1])
+      streams[2].wait_stream(streams[0])
       e1.record(streams[2])
     torch.cuda.synchronize()
 
   run(0, max(W, 1), False)
   run(W, K, True)
+  if len(parts) < 3:      # a partial run (diagnosis): only the time means anything
+    return {'ms': e0.elapsed_time(e1), 'h2d': h2d, 'd2h': d2h}
   last = (K - 1) % n_buf
   if not torch.isfinite(y_host[last]).all() or float(y_host[last].abs().sum()) == 0.0:
     raise SystemExit('e2e: the result copied back to the host is empty')
@@ -723,71 +698,97 @@ def run_sharded(args, torch, dist, device, world):
 def run_e2e_sharded(torch, dist, work, exchange, ev_host_mine, shape, W, K, device, want_last):
   """End to end on N ranks: per step a rank copies ITS OWN n/N spikes of the next step from pinned host memory,
   runs the one-launch step (push to the peers + scatter of the current step) and copies ITS OWN slice of the
-  result to pinned host memory.  Copy-in, compute and copy-out run on three streams; three spike buffers and
-  three result buffers; the K steps are captured in one CUDA graph per rank.  Time: maximum over ranks."""
+  result to pinned host memory.  Copy-in, compute and copy-out run on three streams with three spike buffers and
+  three result buffers; the CUDA runtime and the library are driven directly, step by step.  Time: CUDA events
+  on every rank between two barriers, maximum over ranks."""
+  import ctypes
+  from brainpylib_b200 import _lib
+  rt = ctypes.CDLL('libcudart.so.12')
+  rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+  rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint]
+  rt.cudaEventRecord.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+  rt.cudaStreamWaitEvent.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+
+  def check(code):
+    if code != 0:
+      raise SystemExit(f'CUDA runtime call failed with error {code}')
+
+  streams = [torch.cuda.Stream(device) for _ in range(3)]
+  s_in, s_c, s_out = (ctypes.c_void_p(st.cuda_stream) for st in streams)
   n_buf = 3
   per = ev_host_mine.shape[1]
   ev_buf = [torch.empty(per, dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+  h2d, d2h = 4 * per, 4 * shape[1]
 
-  def build(first, count):
-    done_in, done_c, done_out = {}, {}, {}
-
-    def copy_in(i, s_in):          # spikes of step first + i into ev_buf[i % n_buf]
-      if i >= n_buf:
-        s_in.wait_event(done_c[i - n_buf])         # the launch that pushed this buffer has finished
-      with torch.cuda.stream(s_in):
-        ev_buf[i % n_buf].copy_(ev_host_mine[first + i], non_blocking=True)
-        done_in[i] = torch.cuda.Event()
-        done_in[i].record(s_in)
-
-    def enqueue(i, s_in, s_c, s_out):
-      if i == 0:
-        copy_in(0, s_in)
-        s_c.wait_event(done_in[0])
-        with torch.cuda.stream(s_c):
-          exchange.prime(ev_buf[0], y_buf[0])
-          done_c[0] = torch.cuda.Event()           # the prime launch consumed the spikes of step 0
-          done_c[0].record(s_c)
-      last = i == count - 1
-      if not last:
-        copy_in(i + 1, s_in)
-        s_c.wait_event(done_in[i + 1])
-      if i + 1 >= n_buf and not last:
-        s_c.wait_event(done_out[i + 1 - n_buf])    # y_buf[(i + 1) % n_buf] is zero-filled by this launch
-      with torch.cuda.stream(s_c):
-        exchange.step(work['data'], work['indices'], work['indptr'], y_buf[i % n_buf],
-                      None if last else y_buf[(i + 1) % n_buf], None if last else ev_buf[(i + 1) % n_buf])
-        done_c[i + 1] = torch.cuda.Event()         # launch i consumed the spikes of step i + 1 (pushed them)
-        done_c[i + 1].record(s_c)
-      s_out.wait_event(done_c[i + 1])
-      with torch.cuda.stream(s_out):
-        y_host[i % n_buf].copy_(y_buf[i % n_buf], non_blocking=True)
-        done_out[i] = torch.cuda.Event()
-        done_out[i].record(s_out)
-    return capture_e2e(torch, device, count, enqueue)
-
-  warm, graph = build(0, max(W, 1)), build(W, K)
-  warm.replay()
+  def new_event():
+    e = ctypes.c_void_p()
+    check(rt.cudaEventCreateWithFlags(ctypes.byref(e), 2))   # cudaEventDisableTiming
+    return e
+  # done_in[b]: spikes copied into ev_buf[b]; pushed[b]: the launch that pushed ev_buf[b] has finished;
+  # done_c[b]: the launch that scattered into y_buf[b] has finished; done_out[b]: y_buf[b] has reached the host
+  done_in, pushed, done_c, done_out = ([new_event() for _ in range(n_buf)] for _ in range(4))
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  torch.cuda.synchronize()
-  dist.barrier()
-  torch.cuda.synchronize()
-  e0.record()
-  graph.replay()
-  e1.record()
-  torch.cuda.synchronize()
-  dist.barrier()
+
+  # everything a step needs is marshalled once: no Python work between the launches beyond the calls themselves
+  ev_ptr = [t.data_ptr() for t in ev_buf]
+  y_ptr = [t.data_ptr() for t in y_buf]
+  yh_ptr = [t.data_ptr() for t in y_host]
+  host_base = ev_host_mine.data_ptr()
+  mid_step = [exchange.step_call(work['data'], work['indices'], work['indptr'], y_buf[b], y_buf[(b + 1) % n_buf],
+                                 ev_buf[(b + 1) % n_buf], s_c) for b in range(n_buf)]
+  last_step = [exchange.step_call(work['data'], work['indices'], work['indptr'], y_buf[b], None, None, s_c)
+               for b in range(n_buf)]
+
+  def copy_in(first, j):            # spikes of step first + j into ev_buf[j % n_buf]
+    b = j % n_buf
+    if j >= n_buf:
+      check(rt.cudaStreamWaitEvent(s_in, pushed[b], 0))
+    check(rt.cudaMemcpyAsync(ev_ptr[b], host_base + (first + j) * h2d, h2d, 1, s_in))
+    check(rt.cudaEventRecord(done_in[b], s_in))
+
+  def run(first, count, timed):
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    if timed:
+      e0.record(streams[0])
+    copy_in(first, 0)
+    check(rt.cudaStreamWaitEvent(s_c, done_in[0], 0))
+    exchange.prime(ev_buf[0], y_buf[0], stream=s_c)
+    check(rt.cudaEventRecord(pushed[0], s_c))
+    for i in range(count):
+      last = i == count - 1
+      b, nb = i % n_buf, (i + 1) % n_buf
+      if not last:
+        copy_in(first, i + 1)
+        check(rt.cudaStreamWaitEvent(s_c, done_in[nb], 0))
+        if i + 1 >= n_buf:
+          check(rt.cudaStreamWaitEvent(s_c, done_out[nb], 0))   # y_buf[nb] is zero-filled by this launch
+      (last_step if last else mid_step)[b]()
+      if not last:
+        check(rt.cudaEventRecord(pushed[nb], s_c))
+      check(rt.cudaEventRecord(done_c[b], s_c))
+      check(rt.cudaStreamWaitEvent(s_out, done_c[b], 0))
+      check(rt.cudaMemcpyAsync(yh_ptr[b], y_ptr[b], d2h, 2, s_out))
+      check(rt.cudaEventRecord(done_out[b], s_out))
+    _lib.check_status()
+    if timed:
+      streams[2].wait_stream(streams[1])
+      e1.record(streams[2])
+    torch.cuda.synchronize()
+    dist.barrier()
+
+  run(0, max(W, 1), False)
+  run(W, K, True)
   t = torch.tensor([e0.elapsed_time(e1)], device=device)
   dist.all_reduce(t, op=dist.ReduceOp.MAX)
   exchange.check_all(dist)
   last = (K - 1) % n_buf
   if not torch.allclose(y_host[last].to(device), want_last, rtol=1e-5, atol=1e-2):
     raise SystemExit('e2e: the slice copied back to the host differs from the stand-alone operator result')
-  warm.reset()
-  graph.reset()
-  return {'ms': t.item(), 'h2d': 4 * per, 'd2h': 4 * shape[1]}
+  return {'ms': t.item(), 'h2d': h2d, 'd2h': d2h}
 
 
 def main():

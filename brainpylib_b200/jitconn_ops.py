@@ -83,11 +83,12 @@ def event_matvec_raw(events, *, kind, w1=0., w2=0., conn_prob, shape, seed, tran
   return out
 
 
-def matmat_raw(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None):
-  """Primitive ``matmat_prob_{uniform,normal}`` (version 'v1'): ``Y = X @ M``."""
+def matmat_raw(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None, version='v1'):
+  """Primitive ``matmat_prob_{uniform,normal}``: ``Y = X @ M``; target ``gpu_matmat_prob_prob_<kind>_<T>_<version>``
+  as brainpylib/_src/jitconn_ops/matmat.py:443-466 builds it."""
   m, k = matrix.shape
   opaque = gpu_ops.build_matmat_jit_prob_descriptor1(m, k, shape[1], seed, _log_p(conn_prob), w1, w2)
-  name = 'gpu_matmat_prob_prob_' + kind + float_suffix(matrix.dtype) + '_v1'
+  name = 'gpu_matmat_prob_prob_' + kind + float_suffix(matrix.dtype) + '_' + version
   if out is None:
     out = torch.empty((m, shape[1]), dtype=matrix.dtype, device=matrix.device)
   _lib.call(name, [matrix, out], opaque, device=matrix.device)
@@ -160,9 +161,48 @@ def _matvec(vector, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_para
   return matvec_raw(vector, **kw)
 
 
-def _event_matvec(events, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_parallel):
+def event_matvec_v1_raw(event_ids, event_num, *, kind, w1, w2, conn_prob, n_row, n_col, seed, dtype=torch.float32,
+                        out=None):
+  """Primitive of the counter-based scheme: target ``gpu_event_matvec_prob_{homo,uniform,normal}_{float,double}``
+  (lib/gpu_ops.cc:107-112) on the event list ``event_info`` returns.  The descriptor carries the RAW probability
+  (lib/gpu_jitconn_event_matvec.cu:36: ``lfsr113_double(...) < conn_prob``)."""
+  if kind == 'homo':
+    opaque = gpu_ops.build_jitconn_prob_homo_descriptor(n_row, n_col, seed, conn_prob)
+  elif kind == 'uniform':
+    opaque = gpu_ops.build_jitconn_prob_uniform_descriptor(n_row, n_col, seed, conn_prob, w1, w2)
+  else:
+    opaque = gpu_ops.build_jitconn_prob_normal_descriptor(n_row, n_col, seed, conn_prob, w1, w2)
+  if out is None:
+    out = torch.empty(n_row, dtype=dtype, device=event_ids.device)
+  num = event_num.reshape(1) if event_num.ndim == 0 else event_num
+  _lib.call('gpu_event_matvec_prob_' + kind + float_suffix(dtype), [event_ids, num, out], opaque, device=event_ids.device)
+  return out
+
+
+def _event_matvec_v1(events, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_parallel):
+  """``version='v1'`` of the event products (no counterpart in the reference's Python layer, which never builds
+  these target names): spike compaction with ``event_info``, then the counter-based kernel.  The matrix is a
+  function of ``(seed, row, column)`` alone; ``transpose`` only swaps which dimension is the output."""
+  from .event_ops import event_info
+  if not outdim_parallel:
+    raise ValueError("version='v1' computes one output per thread (outdim_parallel=True) only")
+  if torch.is_grad_enabled() and events.requires_grad:
+    raise NotImplementedError("version='v1' of the event products has no differentiation rule; use 'v2'")
+  n_row, n_col = (shape[1], shape[0]) if transpose else shape
+  ids, num = event_info(events)
+  out_dtype = torch.float32 if events.dtype == torch.bool else events.dtype
+  return event_matvec_v1_raw(ids, num, kind=kind, w1=w1, w2=w2, conn_prob=conn_prob, n_row=int(n_row), n_col=int(n_col),
+                             seed=_seed(seed) & 0xFFFFFFFF, dtype=out_dtype)
+
+
+def _event_matvec(events, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_parallel, version='v2'):
   events = as_tensor(events, device_of(events))
   _check_vector(events, shape, transpose, 'events')
+  if version not in ('v1', 'v2'):
+    raise ValueError(f"version must be 'v1' or 'v2', got {version!r}")
+  if version == 'v1':
+    return _event_matvec_v1(contiguous(events), kind, w1, w2, conn_prob, (int(shape[0]), int(shape[1])), seed,
+                            bool(transpose), bool(outdim_parallel))
   kw = dict(kind=kind, w1=w1, w2=w2, conn_prob=conn_prob, shape=(int(shape[0]), int(shape[1])), seed=_seed(seed),
             transpose=bool(transpose), outdim_parallel=bool(outdim_parallel))
   events = contiguous(events)
@@ -257,10 +297,13 @@ def event_matvec_prob_conn_homo_weight(
     seed: Optional[int] = None,
     transpose: bool = False,
     outdim_parallel: bool = True,
+    version: str = 'v2',
 ) -> torch.Tensor:
   r"""Event-driven :math:`y = M @ \mathrm{events}` with the scalar ``weight`` at each
-  connection.  ``events`` is bool or floating point (its non-zero entries are the events)."""
-  r = _event_matvec(events, 'homo', 0., 0., conn_prob, shape, seed, transpose, outdim_parallel)
+  connection.  ``events`` is bool or floating point (its non-zero entries are the events).
+  ``version='v1'`` (not reachable from the reference's Python layer) uses the counter-based generator of
+  lib/kernel_helpers_random.cuh: another random matrix, defined entry by entry by ``(seed, row, column)``."""
+  r = _event_matvec(events, 'homo', 0., 0., conn_prob, shape, seed, transpose, outdim_parallel, version)
   weight = as_tensor(weight, r.device, r.dtype)
   return r * weight
 
@@ -275,11 +318,13 @@ def event_matvec_prob_conn_uniform_weight(
     seed: Optional[int] = None,
     transpose: bool = False,
     outdim_parallel: bool = True,
+    version: str = 'v2',
 ) -> torch.Tensor:
-  r"""Event-driven product with connection values drawn uniformly from ``[w_low, w_high)``."""
+  r"""Event-driven product with connection values drawn uniformly from ``[w_low, w_high)``.
+  ``version``: see :func:`event_matvec_prob_conn_homo_weight`."""
   assert w_high > w_low
   return _event_matvec(events, 'uniform', w_low, w_high - w_low, conn_prob, shape, seed, transpose,
-                       outdim_parallel)
+                       outdim_parallel, version)
 
 
 def event_matvec_prob_conn_normal_weight(
@@ -292,9 +337,11 @@ def event_matvec_prob_conn_normal_weight(
     seed: Optional[int] = None,
     transpose: bool = False,
     outdim_parallel: bool = True,
+    version: str = 'v2',
 ) -> torch.Tensor:
-  r"""Event-driven product with connection values drawn from ``N(w_mu, w_sigma)``."""
-  return _event_matvec(events, 'normal', w_mu, w_sigma, conn_prob, shape, seed, transpose, outdim_parallel)
+  r"""Event-driven product with connection values drawn from ``N(w_mu, w_sigma)``.
+  ``version``: see :func:`event_matvec_prob_conn_homo_weight`."""
+  return _event_matvec(events, 'normal', w_mu, w_sigma, conn_prob, shape, seed, transpose, outdim_parallel, version)
 
 
 def _matmat(matrix, kind, w1, w2, conn_prob, shape, seed, version, what):
@@ -307,13 +354,15 @@ def _matmat(matrix, kind, w1, w2, conn_prob, shape, seed, version, what):
     raise ValueError(f'Shape mismatch, X {tuple(matrix.shape)} @ M ({shape},).')
   if seed is None:
     raise ValueError('Seed cannot be none.')
-  if version != 'v1':
-    raise ValueError("only version='v1' (one random stream per output column) is built; the reference's 'v2'/'v3' "
-                     "generate different matrices")
+  # the reference registers v1 for both kinds and v2 / v3 for normal weights only (lib/gpu_ops.cc:166-174); each
+  # version generates its own matrix
+  if version not in (('v1', 'v2', 'v3') if kind == 'normal' else ('v1',)):
+    raise ValueError(f"version must be 'v1'" + (", 'v2' or 'v3'" if kind == 'normal' else '') + f' for {kind} weights, '
+                     f'got {version!r}')
   if not matrix.dtype.is_floating_point:
     matrix = matrix.to(torch.float32)
   return matmat_raw(contiguous(matrix), kind=kind, w1=w1, w2=w2, conn_prob=conn_prob,
-                    shape=(int(shape[0]), int(shape[1])), seed=int(seed))
+                    shape=(int(shape[0]), int(shape[1])), seed=int(seed), version=version)
 
 
 def matmat_prob_conn_uniform_weight(
@@ -345,6 +394,8 @@ def matmat_prob_conn_normal_weight(
     version: str = 'v1'
 ) -> torch.Tensor:
   r"""Perform :math:`Y = X @ M` with :math:`M` (``shape``) generated just in time, values
-  from ``N(w_mu, w_sigma)``."""
+  from ``N(w_mu, w_sigma)``.  ``version``: 'v1' (default; one random stream per output column, equal row by row
+  to ``matvec_prob_conn_normal_weight(..., transpose=True)``), 'v2' (32 streams per column) or 'v3' (streams per
+  row of ``matrix``): three different random matrices, as in the reference."""
   return _matmat(matrix, 'normal', w_mu, w_sigma, conn_prob, shape, seed, version,
                  'vector should be a 2D matrix.')

@@ -132,9 +132,19 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   replaces lib/gpu_jitconn_event_matvec.cu:111-135,251-278,399-426 and
  *   lib/gpu_jitconn_event_matvec_atomic.cu:61-85,120-147,181-208 (lib/gpu_ops.cc:115-140)
  *   opaque  as above; buffers [events E(n_col), y T(n_row)]
+ * gpu_event_matvec_prob_{homo,uniform,normal}_{float,double}      (the counter-based "v1" scheme)
+ *   replaces lib/gpu_jitconn_event_matvec.cu:10-51,138-183,281-331 + lib/kernel_helpers_random.cuh:12-71
+ *   (lib/gpu_ops.cc:107-112).  Connection (row r, column c) exists iff lfsr113(seed + n_col * r + c) < prob (RAW
+ *   probability in the descriptor); its weight comes from taus88 on the same seed.  Only listed events are visited.
+ *   opaque  JITConnProb{Homo,Uniform,Normal}Descriptor; buffers [event_ids i32, event_num i32(1), y T(n_row)].
+ *   The count is read on the device (the reference's wrapper dereferences the device pointer on the host).
  * gpu_matmat_prob_prob_{normal,uniform}_{float,double}_v1
  *   replaces lib/gpu_jitconn_matmat.cu:279-317,364-402 (lib/gpu_ops.cc:171-174)
  *   opaque  MatMatJITProbDescriptor1{m,k,n,seed,log_p,w1,w2}; buffers [X T(m,k), Y T(m,n)] row-major
+ * gpu_matmat_prob_prob_normal_{float,double}_{v2,v3}
+ *   replace lib/gpu_jitconn_matmat.cu:138-231 (v2: 32 streams per column, one per range of ceil(k / 32) rows) and
+ *   :19-135 (v3: one stream per row of X, pairs shared by a block of rows); registered lib/gpu_ops.cc:166-169.
+ *   Each generates its own matrix, different from v1's.  Same opaque and buffers.
  *
  * nonzero_{bool,int,long,float,double}   replaces lib/gpu_event_info.cu:48-118 (lib/gpu_ops.cc:72-76)
  *   opaque NonZeroDescriptor{event_size, batch_size}
@@ -166,6 +176,7 @@ void bpl_profile_scatter_events(void *before, void *after);
 #define BPL_FOR_EACH_TARGET(X)                                      \
     BPL_FOR_EACH_TE(X, event_csr_matvec_homo)                       \
     BPL_FOR_EACH_TE(X, event_csr_matvec_heter)                      \
+    X(event_csr_matvec_heter_float_float_noalloc)                   \
     X(event_cbcsr_matvec_heter_float_bool) X(event_cbcsr_matvec_heter_float_float) \
     BPL_FOR_EACH_T(X, csr_matvec_homo_scalar)                       \
     BPL_FOR_EACH_T(X, csr_matvec_homo_vector)                       \
@@ -184,6 +195,9 @@ void bpl_profile_scatter_events(void *before, void *after);
     BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_homo_v2)               \
     BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_uniform_v2)            \
     BPL_FOR_EACH_T(X, gpu_matvec_atomic_prob_normal_v2)             \
+    BPL_FOR_EACH_T(X, gpu_event_matvec_prob_homo)                   \
+    BPL_FOR_EACH_T(X, gpu_event_matvec_prob_uniform)                \
+    BPL_FOR_EACH_T(X, gpu_event_matvec_prob_normal)                 \
     BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_homo_v2)               \
     BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_uniform_v2)            \
     BPL_FOR_EACH_TE(X, gpu_event_matvec_prob_normal_v2)             \
@@ -192,6 +206,10 @@ void bpl_profile_scatter_events(void *before, void *after);
     BPL_FOR_EACH_TE(X, gpu_event_matvec_atomic_prob_normal_v2)      \
     X(gpu_matmat_prob_prob_normal_float_v1)                         \
     X(gpu_matmat_prob_prob_normal_double_v1)                        \
+    X(gpu_matmat_prob_prob_normal_float_v2)                         \
+    X(gpu_matmat_prob_prob_normal_double_v2)                        \
+    X(gpu_matmat_prob_prob_normal_float_v3)                         \
+    X(gpu_matmat_prob_prob_normal_double_v3)                        \
     X(gpu_matmat_prob_prob_uniform_float_v1)                        \
     X(gpu_matmat_prob_prob_uniform_double_v1)                       \
     X(nonzero_bool) X(nonzero_int) X(nonzero_long) X(nonzero_float) X(nonzero_double) \

@@ -132,6 +132,20 @@ def count_active_synapses(indptr, events):
     _ptr(indptr), _ptr(events), ctypes.c_int(_event_kind(events)), ctypes.c_uint32(indptr.shape[0] - 1)))
 
 
+def jitconn_event_matvec_v1(event_ids, event_num, *, kind, w1=0., w2=0., conn_prob, n_row, n_col, seed,
+                            dtype=np.float32):
+  """Counter-based event product (see ``oracle_jitconn_event_v1`` in synaptic_oracle.c).  ``conn_prob``, ``w1``,
+  ``w2`` are rounded to float32 first, as the descriptor builders do."""
+  ids = np.ascontiguousarray(event_ids, dtype=np.int32)
+  out = np.empty(n_row, dtype=dtype)
+  f32 = lambda v: float(np.float32(v))
+  lib().oracle_jitconn_event_v1(_ptr(ids), ctypes.c_int32(int(event_num)), ctypes.c_uint32(seed & 0xFFFFFFFF),
+                                ctypes.c_double(f32(conn_prob)), ctypes.c_int(kind), ctypes.c_double(f32(w1)),
+                                ctypes.c_double(f32(w2)), ctypes.c_uint32(n_row), ctypes.c_uint32(n_col),
+                                ctypes.c_int(int(np.dtype(dtype) == np.float64)), _ptr(out))
+  return out
+
+
 def descriptor_log_p(conn_prob):
   """``log(1 - p)`` as the GPU kernels receive it: a float64 that holds a
   float32-rounded value (brainpylib/_src/jitconn_ops/matvec.py:346-349 computes a

@@ -124,3 +124,60 @@ uint64_t oracle_count_active_synapses(const uint32_t *indptr, const void *events
         if (event_is_set(events, ev_kind, r)) s += indptr[r + 1] - indptr[r];
     return s;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Counter-based ("v1") just-in-time-connectivity event product, restated from the kernel text
+ * lib/gpu_jitconn_event_matvec.cu:10-51 (homo), :138-183 (uniform), :281-331 (normal) with the
+ * generators of lib/kernel_helpers_random.cuh:12-71 (one step of L'Ecuyer's lfsr113 / taus88 from
+ * the states seed + 1, + 7, + 15 [, + 127]):
+ *   y[r] = sum over listed events c of [lfsr113(seed + n_col * r + c) < prob] * w
+ * The reference's wrappers cannot run (they dereference the device count on the host), so this
+ * restatement of the kernel arithmetic is the only pin these targets have.  The products that the
+ * device compiler fuses are written as fma() here.
+ * ------------------------------------------------------------------------------------------ */
+#include <math.h>
+
+static double v1_lfsr113(uint32_t seed) {
+    uint32_t z1 = seed + 1u, z2 = seed + 7u, z3 = seed + 15u, z4 = seed + 127u, b;
+    b = ((z1 << 6) ^ z1) >> 13;   z1 = ((z1 & 4294967294u) << 18) ^ b;
+    b = ((z2 << 2) ^ z2) >> 27;   z2 = ((z2 & 4294967288u) << 2) ^ b;
+    b = ((z3 << 13) ^ z3) >> 21;  z3 = ((z3 & 4294967280u) << 7) ^ b;
+    b = ((z4 << 3) ^ z4) >> 12;   z4 = ((z4 & 4294967168u) << 13) ^ b;
+    return (z1 ^ z2 ^ z3 ^ z4) * 2.3283064365386963e-10;
+}
+
+static double v1_taus88_step(uint32_t *s1, uint32_t *s2, uint32_t *s3) {
+    uint32_t b;
+    b = (((*s1 << 13) ^ *s1) >> 19);  *s1 = (((*s1 & 4294967294u) << 12) ^ b);
+    b = (((*s2 << 2) ^ *s2) >> 25);   *s2 = (((*s2 & 4294967288u) << 4) ^ b);
+    b = (((*s3 << 3) ^ *s3) >> 11);   *s3 = (((*s3 & 4294967280u) << 17) ^ b);
+    return ((*s1 ^ *s2 ^ *s3) * 2.3283064365386963e-10);
+}
+
+/* kind: 0 homo, 1 uniform (w1 = w_min, w2 = w_range), 2 normal (w1 = mu, w2 = sigma); out_f64: 0 float, 1 double */
+void oracle_jitconn_event_v1(const int32_t *event_ids, int32_t event_num, uint32_t conn_seed, double prob,
+                             int kind, double w1, double w2, uint32_t n_row, uint32_t n_col, int out_f64,
+                             void *out) {
+    for (uint32_t r = 0; r < n_row; ++r) {
+        const uint32_t seed_base = conn_seed + n_col * r;
+        float sum_f = 0.0f;
+        double sum_d = 0.0;
+        for (int32_t i = 0; i < event_num; ++i) {
+            const uint32_t seed = seed_base + (uint32_t) event_ids[i];
+            if (!(v1_lfsr113(seed) < prob)) continue;
+            double w = 1.0;
+            if (kind != 0) {
+                uint32_t s1 = seed + 1u, s2 = seed + 7u, s3 = seed + 15u;
+                const double u = v1_taus88_step(&s1, &s2, &s3);
+                if (kind == 1) {
+                    w = fma(u, w2, w1);
+                } else {
+                    const double v = v1_taus88_step(&s1, &s2, &s3);
+                    w = fma(sqrt(-2 * log(u)) * cos(2 * 3.14159265358979323846 * v), w2, w1);
+                }
+            }
+            if (out_f64) sum_d += w; else sum_f = (float) ((double) sum_f + w);
+        }
+        if (out_f64) ((double *) out)[r] = sum_d; else ((float *) out)[r] = sum_f;
+    }
+}

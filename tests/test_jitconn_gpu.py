@@ -315,3 +315,110 @@ def test_matmat_column_shards_concatenate_to_the_full_product(cuda, kind, world)
   parts = [sharded.matmat_column_shard(X, rank=r, world=world, **kw) for r in range(world)]
   assert sum(p.shape[1] for p in parts) == n
   assert torch.equal(torch.cat(parts, dim=1), full)
+
+
+# ------------------------------------------------------------------------------------------
+# matmat versions 'v2' and 'v3': other random matrices than 'v1', each bit for bit against its own reference
+# kernel (lib/gpu_jitconn_matmat.cu:138-231 and :19-135).
+# ------------------------------------------------------------------------------------------
+@pytest.mark.skipif(not ref.available_gpu(), reason='oracle/_ref/libref_gpu.so not built')
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+@pytest.mark.parametrize('m', [5, 8, 16, 24, 32, 40, 64])
+def test_matmat_v2_equals_reference_kernel(cuda, m, dtype):
+  """The reference reads X beyond its m rows when m is not a multiple of its row group (and in padding warps):
+  it gets a zero-padded copy large enough for every such read; only the store is guarded there."""
+  tname = 'float' if dtype == torch.float32 else 'double'
+  for shape, prob in (((100, 200), 0.1), ((1000, 7), 0.02), ((33, 257), 0.3)):
+    X = torch.randn(m, shape[0], dtype=dtype, device=cuda, generator=torch.Generator(device=cuda).manual_seed(m))
+    Y = bpl.matmat_prob_conn_normal_weight(X, w_mu=0.1, w_sigma=0.02, conn_prob=prob, shape=shape, seed=11, version='v2')
+    pad = torch.zeros((m + 64 + 16 * 32) * shape[0], dtype=dtype, device=cuda)
+    pad[: m * shape[0]] = X.reshape(-1)
+    Y_ref = torch.full((m, shape[1]), float('nan'), dtype=dtype, device=cuda)
+    opaque = gpu_ops.build_matmat_jit_prob_descriptor1(m, shape[0], shape[1], 11, jitconn_ops._log_p(prob), 0.1, 0.02)
+    ref.gpu_call(f'gpu_matmat_prob_prob_normal_{tname}_v2', [pad, Y_ref], opaque)
+    assert torch.equal(Y, Y_ref), (m, shape, (Y - Y_ref).abs().max().item())
+    assert not torch.equal(Y, bpl.matmat_prob_conn_normal_weight(X, w_mu=0.1, w_sigma=0.02, conn_prob=prob, shape=shape,
+                                                                 seed=11))   # another matrix than v1's
+
+
+@pytest.mark.skipif(not ref.available_gpu(), reason='oracle/_ref/libref_gpu.so not built')
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+def test_matmat_v3_equals_reference_kernel_where_the_reference_is_defined(cuda, dtype):
+  """m = 32 only: one warp per block.  For other m the reference either never terminates (rows beyond m never see
+  the position advance, lib/gpu_jitconn_matmat.cu:40-55) or races on its shared arrays (no barrier between a
+  round's reads and the next round's writes), so it is not run there."""
+  tname = 'float' if dtype == torch.float32 else 'double'
+  m = 32
+  for shape, prob in (((100, 200), 0.1), ((1000, 7), 0.02), ((33, 257), 0.3)):
+    X = torch.randn(m, shape[0], dtype=dtype, device=cuda, generator=torch.Generator(device=cuda).manual_seed(3))
+    Y = bpl.matmat_prob_conn_normal_weight(X, w_mu=0.1, w_sigma=0.02, conn_prob=prob, shape=shape, seed=11, version='v3')
+    Y_ref = torch.full((m, shape[1]), float('nan'), dtype=dtype, device=cuda)
+    opaque = gpu_ops.build_matmat_jit_prob_descriptor1(m, shape[0], shape[1], 11, jitconn_ops._log_p(prob), 0.1, 0.02)
+    ref.gpu_call(f'gpu_matmat_prob_prob_normal_{tname}_v3', [X, Y_ref], opaque)
+    assert torch.equal(Y, Y_ref), (shape, (Y - Y_ref).abs().max().item())
+
+
+def test_matmat_v3_and_v2_relations_where_the_reference_cannot_run(cuda):
+  """Any m: deterministic; v3's rows of one block share one connectivity, so scaling X scales Y exactly (power of
+  two) and a row of zeros gives zeros; v2 is linear in X in the same sense."""
+  for version in ('v2', 'v3'):
+    for m in (5, 33, 70, 600):
+      shape, prob = (300, 50), 0.05
+      X = torch.randn(m, shape[0], device=cuda, generator=torch.Generator(device=cuda).manual_seed(m))
+      kw = dict(w_mu=0., w_sigma=0.5, conn_prob=prob, shape=shape, seed=5, version=version)
+      Y = bpl.matmat_prob_conn_normal_weight(X, **kw)
+      assert Y.shape == (m, shape[1]) and torch.isfinite(Y).all() and Y.abs().sum() > 0
+      assert torch.equal(Y, bpl.matmat_prob_conn_normal_weight(X, **kw))
+      assert torch.equal(bpl.matmat_prob_conn_normal_weight(4 * X, **kw), 4 * Y)
+      X0 = X.clone()
+      X0[m // 2] = 0
+      assert not bpl.matmat_prob_conn_normal_weight(X0, **kw)[m // 2].any()
+
+
+# ------------------------------------------------------------------------------------------
+# The counter-based ("v1") event products: gpu_event_matvec_prob_{homo,uniform,normal}_{float,double}.  The
+# reference's wrappers for these targets cannot run (host dereference of the device-side event count), so the pin
+# is the CPU restatement of the kernel text (oracle.cpu.jitconn_event_matvec_v1): integer-exact generators, so
+# homogeneous and uniform results must agree bit for bit; normal weights go through log / sqrt / cos in double on
+# both sides and are compared at 1e-6 relative.
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+@pytest.mark.parametrize('kind,w1,w2', [('homo', 0., 0.), ('uniform', -0.1, 0.2), ('normal', 0.05, 0.01)])
+@pytest.mark.parametrize('shape,prob,rate', [((100, 200), 0.1, 0.2), ((1000, 10), 0.4, 0.5), ((3, 3000), 0.02, 0.3),
+                                             ((700, 900), 0.05, 0.0), ((513, 300), 0.5, 1.0)])
+def test_counter_based_event_matvec_matches_the_kernel_text(cuda, shape, prob, rate, kind, w1, w2, dtype):
+  rng = np.random.default_rng(17)
+  seed = 2_654_435_761                      # a large seed: the one-step generators mix small seeds poorly
+  ev = rng.random(shape[1]) < rate
+  ids = np.flatnonzero(ev).astype(np.int32)
+  np_dtype = np.float32 if dtype == torch.float32 else np.float64
+  want = cpu.jitconn_event_matvec_v1(ids, ids.shape[0], kind=['homo', 'uniform', 'normal'].index(kind), w1=w1, w2=w2,
+                                     conn_prob=prob, n_row=shape[0], n_col=shape[1], seed=seed, dtype=np_dtype)
+  events = torch.as_tensor(ev).to(cuda) if dtype == torch.float32 else torch.as_tensor(ev.astype(np.float64)).to(cuda)
+  ops = {'homo': lambda e, **kw: bpl.event_matvec_prob_conn_homo_weight(e, 1.0, **kw),
+         'uniform': lambda e, **kw: bpl.event_matvec_prob_conn_uniform_weight(e, w_low=w1, w_high=w1 + w2, **kw),
+         'normal': lambda e, **kw: bpl.event_matvec_prob_conn_normal_weight(e, w_mu=w1, w_sigma=w2, **kw)}
+  y = ops[kind](events, conn_prob=prob, shape=shape, seed=seed, version='v1')
+  assert y.dtype == dtype and y.shape == (shape[0],)
+  y = y.cpu().numpy()
+  if kind == 'normal':
+    np.testing.assert_allclose(y, want, rtol=1e-6, atol=1e-6)
+  else:
+    assert y.tobytes() == want.tobytes(), np.abs(y - want).max()
+  # (the density of the generated matrix is NOT asserted: one step of lfsr113 from a raw seed mixes poorly, e.g. 6 %
+  #  instead of 40 % for 10 input columns; that is the generator the reference's kernel text defines)
+  # transpose only swaps which side is the output: (shape, T) == (shape[::-1], not T), as for v2
+  if rate > 0 and kind != 'normal':
+    ev_t = rng.random(shape[0]) < rate
+    e_t = torch.as_tensor(ev_t).to(cuda) if dtype == torch.float32 else torch.as_tensor(ev_t.astype(np.float64)).to(cuda)
+    a = ops[kind](e_t, conn_prob=prob, shape=shape, seed=seed, version='v1', transpose=True)
+    b = ops[kind](e_t, conn_prob=prob, shape=shape[::-1], seed=seed, version='v1', transpose=False)
+    assert torch.equal(a, b)
+
+
+def test_counter_based_event_matvec_refuses_what_it_has_no_kernel_for(cuda):
+  ev = torch.ones(10, dtype=torch.bool, device=cuda)
+  with pytest.raises(ValueError):
+    bpl.event_matvec_prob_conn_homo_weight(ev, 1.0, conn_prob=0.1, shape=(5, 10), seed=1, version='v1', outdim_parallel=False)
+  with pytest.raises(ValueError):
+    bpl.event_matvec_prob_conn_homo_weight(ev, 1.0, conn_prob=0.1, shape=(5, 10), seed=1, version='v3')

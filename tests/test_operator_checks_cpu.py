@@ -56,10 +56,14 @@ def test_shape_checks_raise_the_reference_messages():
     bpl.matvec_prob_conn_uniform_weight(torch.ones(4), w_low=1., w_high=0., conn_prob=0.1, shape=(3, 4), seed=1)
 
 
-def test_versions_that_define_other_matrices_are_refused():
-  with pytest.raises(ValueError, match="only version='v1'"):
+def test_versions_the_reference_does_not_register_are_refused():
+  """lib/gpu_ops.cc:166-174: normal weights have v1, v2 and v3, uniform weights v1 only."""
+  with pytest.raises(ValueError, match="version must be 'v1'"):
+    bpl.matmat_prob_conn_uniform_weight(torch.ones(2, 3), w_low=0., w_high=1., conn_prob=0.1, shape=(3, 3), seed=1,
+                                        version='v2')
+  with pytest.raises(ValueError, match="version must be 'v1'"):
     bpl.matmat_prob_conn_normal_weight(torch.ones(2, 3), w_mu=0., w_sigma=1., conn_prob=0.1, shape=(3, 3), seed=1,
-                                       version='v2')
+                                       version='v4')
   with pytest.raises(AssertionError):
     bpl.matvec_prob_conn_homo_weight(torch.ones(3), 1.0, conn_prob=0.1, shape=(3, 3), seed=1, version='v3')
 

@@ -17,3 +17,5 @@ from . import jitconn_ops
 from .jitconn_ops import *
 from . import compat
 from .compat import *
+from . import neuron_ops
+from .neuron_ops import *

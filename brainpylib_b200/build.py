@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libbrainpylib_b200.so')
 BUILD_DIR = os.path.join(HERE, 'csrc', 'build')
-SOURCES = ['csr_kernels.cu', 'cbcsr_kernels.cu', 'cbcsr_build.cu', 'jitconn_kernels.cu', 'jitconn_matmat_versions.cu', 'jitconn_event_v1.cu', 'scatter_kernels.cu', 'event_info_kernels.cu',
+SOURCES = ['csr_kernels.cu', 'cbcsr_kernels.cu', 'cbcsr_build.cu', 'jitconn_kernels.cu', 'jitconn_matmat_versions.cu', 'jitconn_event_v1.cu', 'neuron_kernels.cu', 'scatter_kernels.cu', 'event_info_kernels.cu',
            'exchange_kernels.cu', 'gpu_ops.cc']
 HEADERS = ['abi.h', 'common.cuh', 'spike_scan.cuh', 'row_scatter.cuh', 'cb_scatter.cuh', os.path.join('..', '..', 'include', 'brainpylib_b200.h')]
 NVCC = os.environ.get('NVCC', 'nvcc')

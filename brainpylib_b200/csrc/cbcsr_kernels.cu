@@ -12,6 +12,8 @@
 //           fixed_point = 0: float accumulators; 1: 32-bit fixed point with 2^scale_log2 units per 1.0
 //   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
 //   workspace: as for event_csr_matvec with transpose (4 KB + 4 B per row): the compacted spike list
+#include <type_traits>
+
 #include "abi.h"
 #include "common.cuh"
 #include "spike_scan.cuh"
@@ -72,8 +74,11 @@ inline uint32_t cb_shares(uint32_t n_blocks) {
     return P < 1 ? 1u : (P > 16 ? 16u : P);
 }
 
+// E = void: the spike list is an operand (buffers [groups, offsets, list, y]; y must already be zero) instead of
+// being compacted from an event vector here.
 template<typename E>
 void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    constexpr bool FROM_LIST = std::is_void<E>::value;
     const CbDescriptor *d = unpack<CbDescriptor>(opaque, opaque_len);
     if (!d) return;
     const uint32_t n_row = d->n_row, n_col = d->n_col, width = d->block_width;
@@ -94,11 +99,11 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     }
     const unsigned char *groups = static_cast<const unsigned char *>(buffers[0]);
     const uint32_t *offsets = static_cast<const uint32_t *>(buffers[1]);
-    const E *events = static_cast<const E *>(buffers[2]);
     float *y = static_cast<float *>(buffers[3]);
-    uint32_t *ws = static_cast<uint32_t *>(buffers[4]);
+    uint32_t *ws = static_cast<uint32_t *>(FROM_LIST ? buffers[2] : buffers[4]);
     if (ws == nullptr) {
-        set_status(BPL_ERR_ARGUMENT, "event_cbcsr_matvec needs a workspace buffer");
+        set_status(BPL_ERR_ARGUMENT, FROM_LIST ? "event_cbcsr_matvec_list needs a spike list"
+                                               : "event_cbcsr_matvec needs a workspace buffer");
         return;
     }
     if (!aligned16(groups)) {
@@ -110,9 +115,13 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     const uint64_t zero_blocks = (static_cast<uint64_t>(n_col) + SCAN_TILE - 1) / SCAN_TILE;
     const uint64_t zero_cap = static_cast<uint64_t>(sm_count()) * 8;
     const uint32_t scan_grid = static_cast<uint32_t>(max(static_cast<uint64_t>(p.n_chunks), min(zero_blocks, zero_cap)));
-    scan_events_kernel<float, E><<<scan_grid, SCAN_THREADS, 0, stream>>>(events, n_row, p.chunk, p.n_chunks, y, n_col,
-                                                                         counts, ids);
-    if (!launch_ok() || n_row == 0) return;
+    if constexpr (!FROM_LIST) {
+        scan_events_kernel<float, E><<<scan_grid, SCAN_THREADS, 0, stream>>>(static_cast<const E *>(buffers[2]), n_row,
+                                                                             p.chunk, p.n_chunks, y, n_col, counts, ids);
+        if (!launch_ok()) return;
+    }
+    (void) scan_grid;
+    if (n_row == 0) return;
     const uint32_t P = cb_shares(n_blocks);
     if (!cb_kernel_configured()) return;
     const CbPlan plan = cb_plan(width);
@@ -144,6 +153,12 @@ void event_cbcsr_matvec_heter_float_bool(bpl_stream_t s, void **b, const char *o
 }
 void event_cbcsr_matvec_heter_float_float(bpl_stream_t s, void **b, const char *o, size_t n) {
     event_cbcsr_impl<float>(s, b, o, n);
+}
+// The scatter alone, from a ready-made spike list (the layout of the workspace: counts[1024], then row ids in chunk
+// segments of bpl-defined size for n_row rows), e.g. the one lif_exp_step_float writes.  y must already be zero.
+//   buffers [groups, offsets, list u32, y f32(n_col)]; opaque as above
+void event_cbcsr_matvec_list_heter_float(bpl_stream_t s, void **b, const char *o, size_t n) {
+    event_cbcsr_impl<void>(s, b, o, n);
 }
 
 // Debugging aid: while `buffer` (device memory, 64 bytes per CTA of the launch) is not null, every

@@ -71,6 +71,9 @@ size_t bpl_build_coo_event_sum_descriptor(uint32_t conn_size, uint32_t post_size
 size_t bpl_build_coo_atomic_sum_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
 size_t bpl_build_coo_atomic_prod_descriptor(uint32_t conn_size, uint32_t post_size, void *out, size_t cap);
 size_t bpl_build_nonzero_descriptor(uint32_t event_size, uint32_t batch_size, void *out, size_t cap);
+size_t bpl_build_lif_exp_descriptor(uint32_t n, uint32_t n_channels, float t, const float *syn_decay, const float *E_rev,
+                                    float ext_input, float V_rest, float V_th, float V_reset, float R, float lif_decay,
+                                    float tau_ref, void *out, size_t cap);
 size_t bpl_build_cbcsr_descriptor(uint32_t n_row, uint32_t n_col, uint32_t block_width, int fixed_point,
                                   int scale_log2, void *out, size_t cap);
 
@@ -109,6 +112,23 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2} (bpl_build_cbcsr_descriptor)
  *   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
  *   workspace: bpl_workspace_bytes() (as for event_csr_matvec with transpose)
+ *
+ * event_cbcsr_matvec_list_heter_float / event_csr_matvec_list_heter_float   (no counterpart in the reference)
+ *   the scatter half alone, driven by a ready-made spike list (counts[1024], then row ids in chunk segments: the
+ *   layout of the event_csr_matvec workspace, written e.g. by lif_exp_step_float); y must already be zero.
+ *   buffers [groups, offsets, list u32, y f32(n_col)] (opaque as event_cbcsr_matvec) resp.
+ *           [data f32, indices u32, indptr u32(n_row + 1), list u32, y f32(n_col)] (opaque {n_row, n_col, n_chunks})
+ *
+ * lif_exp_step_float   (no counterpart in the reference: the caller's side of the step, fused)
+ *   The step pattern of the reference's network example (brainpylib/_src/op_register/tests/ei_net.py:47-72) in one
+ *   launch: per synaptic channel g = g * decay + y (y is then zero-filled for the next step), input += g * (E - V);
+ *   leaky integrate-and-fire update with refractory period, threshold and reset; and the new spikes are compacted
+ *   into the spike list the *_list_* products read, so no event vector has to be scanned and y needs no zero-fill.
+ *   Products and sums are rounded one by one (no fused multiply-add) so that a float32 array implementation agrees
+ *   bit for bit.
+ *   opaque  bpl_build_lif_exp_descriptor()
+ *   buffers [y f32(K, n) in/zeroed, g f32(K, n) in/out, V f32(n) in/out, t_last f32(n) in/out, spikes f32(n) out,
+ *            list u32 out (bpl_workspace_bytes of event_csr_matvec_* with transpose for n rows)]
  *
  * csr_matvec_{homo,heter}_{scalar,vector,adaptive}_{float,double}
  *   replaces lib/gpu_csr_matvec.cu:84-141,195-246,505-560 (lib/gpu_ops.cc:79-92); the three
@@ -178,6 +198,7 @@ void bpl_profile_scatter_events(void *before, void *after);
     BPL_FOR_EACH_TE(X, event_csr_matvec_heter)                      \
     X(event_csr_matvec_heter_float_float_noalloc)                   \
     X(event_cbcsr_matvec_heter_float_bool) X(event_cbcsr_matvec_heter_float_float) \
+    X(event_cbcsr_matvec_list_heter_float) X(event_csr_matvec_list_heter_float) X(lif_exp_step_float) \
     BPL_FOR_EACH_T(X, csr_matvec_homo_scalar)                       \
     BPL_FOR_EACH_T(X, csr_matvec_homo_vector)                       \
     BPL_FOR_EACH_T(X, csr_matvec_homo_adaptive)                     \
@@ -296,10 +317,6 @@ void bpl_sharded_step(bpl_stream_t stream, const void *data, const void *indices
                       int ev_is_float, uint32_t n_local, uint32_t row_offset, void *const *peer_lists,
                       size_t slot_bytes, void *const *peer_flags, void *state, int world, int rank, int slots,
                       uint32_t max_polls);
-/* Scatter half of event_csr_matvec_heter_float_* driven by a ready-made spike list; y must be zero-filled.
- *   buffers [data f32, indices u32, indptr u32(n_row + 1), list u32, y f32(n_col)]
- *   opaque  TripleSizeDescriptor{n_row, n_col, n_chunks} */
-BPL_DECLARE_TARGET(event_csr_matvec_list_heter_float);
 
 /* ---- transposed event product without workspace and without allocation ------------------
  * No counterpart in the reference.  Same computation as event_csr_matvec_heter_float_float

@@ -47,3 +47,16 @@ def float_suffix(dtype):
   if dtype == torch.float64:
     return '_double'
   raise TypeError(f'Only support float32 and float64. But we got {dtype}.')
+
+
+def loop_vmap(apply, info, in_dims, args):
+  """Batching rule shared by every operator: the reference registers the same for all of its primitives
+  (`register_general_batching`, brainpylib/_src/op_register/utils.py:17-38: a scan over the batch); here a Python
+  loop over the batch dimension, one kernel launch per batch entry, results stacked along dimension 0."""
+  outs = []
+  for b in range(info.batch_size):
+    # non-tensor arguments (shapes, flags, keyword dictionaries) carry a pytree of None as their in_dim
+    sliced = [contiguous(a.select(d, b)) if isinstance(a, torch.Tensor) and isinstance(d, int) else a
+              for a, d in zip(args, in_dims)]
+    outs.append(apply(*sliced))
+  return torch.stack(outs), 0

@@ -12,7 +12,7 @@ import torch
 
 from . import _lib, gpu_ops
 from .errors import GPUOperatorNotFound
-from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_like
+from ._checks import as_tensor, contiguous, device_of, float_suffix, is_int32_like, loop_vmap
 
 __all__ = ['event_csr_matvec', 'event_info', 'ColumnBlockedCSR', 'csr_to_column_blocked', 'prepare_event_csr',
            'event_cbcsr_matvec']
@@ -63,25 +63,32 @@ def event_csr_matvec_raw(data, indices, indptr, events, *, shape, transpose=Fals
 
 
 class _EventCSRMatvec(torch.autograd.Function):
-  """Differentiation rules of brainpylib/_src/event_ops/event_csr_matvec.py:439-463,
-  written as the vector-Jacobian product torch asks for:
+  """Differentiation and batching rules of brainpylib/_src/event_ops/event_csr_matvec.py:439-463.
 
-  * w.r.t. ``events``: ``A^T ct`` (or ``A ct``), i.e. the dense CSR product with the
-    opposite ``transpose`` (:447-451).
-  * w.r.t. homogeneous ``data``: ``<ct, op(1, events)>`` (:457-459).
-  * w.r.t. heterogeneous ``data``: ``events[row] * ct[col]`` if transpose else
-    ``events[col] * ct[row]`` (:461-462).
-  """
+  Reverse mode (the transpose rules, :447-463), written as the vector-Jacobian product torch asks for:
+  * w.r.t. ``events``: ``A^T ct`` (or ``A ct``), i.e. the dense CSR product with the opposite ``transpose``;
+  * w.r.t. homogeneous ``data``: ``<ct, op(1, events)>``;
+  * w.r.t. heterogeneous ``data``: ``events[row] * ct[col]`` if transpose else ``events[col] * ct[row]``.
+  Forward mode (the JVP rules, :439-444): data tangent -> the same event product on ``data_dot``; events tangent
+  -> the dense CSR product of ``data`` with ``events_dot``, same ``transpose``.
+  Batching: a loop over the batch (what `register_general_batching` does in the reference)."""
 
   @staticmethod
-  def forward(ctx, data, indices, indptr, events, shape, transpose):
-    ctx.save_for_backward(data, indices, indptr, events)
-    ctx.shape, ctx.transpose = shape, transpose
+  def forward(data, indices, indptr, events, shape, transpose):
     return event_csr_matvec_raw(data, indices, indptr, events, shape=shape, transpose=transpose)
 
   @staticmethod
+  def setup_context(ctx, inputs, output):
+    data, indices, indptr, events, shape, transpose = inputs
+    ctx.save_for_backward(data, indices, indptr, events)
+    ctx.save_for_forward(data, indices, indptr, events)
+    ctx.shape, ctx.transpose = shape, transpose
+
+  # The rules call the operators through their autograd functions, not the raw kernels: under torch.func
+  # transforms the tangents and cotangents arrive wrapped, and only `apply` knows how to unwrap them.
+  @staticmethod
   def backward(ctx, ct):
-    from .sparse_ops import csr_matvec_raw, csr_to_coo
+    from .sparse_ops import _CSRMatvec, csr_to_coo
     data, indices, indptr, events = ctx.saved_tensors
     shape, transpose = ctx.shape, ctx.transpose
     ct = contiguous(ct)
@@ -89,15 +96,32 @@ class _EventCSRMatvec(torch.autograd.Function):
     if ctx.needs_input_grad[0]:
       if data.shape[0] == 1:
         ones = torch.ones(1, dtype=data.dtype, device=data.device)
-        r = event_csr_matvec_raw(ones, indices, indptr, events, shape=shape, transpose=transpose)
+        r = _EventCSRMatvec.apply(ones, indices, indptr, events, shape, transpose)
         g_data = torch.dot(ct, r).reshape(1)
       else:
         row, col = csr_to_coo(indices, indptr)
         ev = events.to(data.dtype)
         g_data = ev[row] * ct[col] if transpose else ev[col] * ct[row]
     if ctx.needs_input_grad[3]:
-      g_events = csr_matvec_raw(data, indices, indptr, ct, shape=shape, transpose=not transpose)
+      g_events = _CSRMatvec.apply(data, indices, indptr, ct, shape, not transpose, 'vector')
     return g_data, None, None, g_events, None, None
+
+  @staticmethod
+  def jvp(ctx, data_dot, _indices, _indptr, events_dot, _shape, _transpose):
+    from .sparse_ops import _CSRMatvec
+    data, indices, indptr, events = ctx.saved_tensors
+    shape, transpose = ctx.shape, ctx.transpose
+    tangent = None
+    if data_dot is not None:
+      tangent = _EventCSRMatvec.apply(contiguous(data_dot), indices, indptr, events, shape, transpose)
+    if events_dot is not None:
+      t = _CSRMatvec.apply(data, indices, indptr, contiguous(events_dot.to(data.dtype)), shape, transpose, 'vector')
+      tangent = t if tangent is None else tangent + t
+    return tangent
+
+  @staticmethod
+  def vmap(info, in_dims, data, indices, indptr, events, shape, transpose):
+    return loop_vmap(_EventCSRMatvec.apply, info, in_dims, (data, indices, indptr, events, shape, transpose))
 
 
 def event_csr_matvec(
@@ -177,13 +201,13 @@ def event_csr_matvec(
   shape = (int(shape[0]), int(shape[1]))
   data, indices, indptr, events = map(contiguous, (data, indices, indptr, events))
   _target_name(data, events)  # dtype errors before autograd machinery
-  if torch.is_grad_enabled() and (data.requires_grad or events.requires_grad):
-    return _EventCSRMatvec.apply(data, indices, indptr, events, shape, bool(transpose))
-  if prepared is not None and transpose and data.dtype == torch.float32:
+  if prepared is not None and transpose and data.dtype == torch.float32 and \
+      not (torch.is_grad_enabled() and (data.requires_grad or events.requires_grad)):
     if not isinstance(prepared, ColumnBlockedCSR) or prepared.shape != shape or prepared.nse != indices.shape[0]:
       raise ValueError('prepared does not describe this matrix (built from another shape or entry count).')
     return event_cbcsr_matvec_raw(prepared, events)
-  return event_csr_matvec_raw(data, indices, indptr, events, shape=shape, transpose=bool(transpose))
+  # always through the autograd function: it carries the reverse-mode, forward-mode and batching rules
+  return _EventCSRMatvec.apply(data, indices, indptr, events, shape, bool(transpose))
 
 
 _NONZERO_SUFFIX = {torch.bool: '_bool', torch.int32: '_int', torch.int64: '_long', torch.float32: '_float',

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from . import _lib, gpu_ops
-from ._checks import as_tensor, contiguous, device_of, float_suffix
+from ._checks import loop_vmap, as_tensor, contiguous, device_of, float_suffix
 from .errors import GPUOperatorNotFound
 
 __all__ = [
@@ -96,34 +96,79 @@ def matmat_raw(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None, versio
 
 
 class _Matvec(torch.autograd.Function):
-  """Linear in the vector: the cotangent goes through the same operator with
-  ``transpose`` and ``outdim_parallel`` both flipped, which walks the same streams and is
-  therefore exactly ``M^T`` (matvec.py:393-402)."""
+  """Linear in the vector.  Reverse mode: the cotangent goes through the same operator with ``transpose`` and
+  ``outdim_parallel`` both flipped, which walks the same streams and is therefore exactly ``M^T``
+  (matvec.py:393-402).  Forward mode (:371-390): the same operator on the tangent.  Batching: a loop."""
 
   @staticmethod
-  def forward(ctx, vector, kw):
-    ctx.kw = kw
+  def forward(vector, kw):
     return matvec_raw(vector, **kw)
 
   @staticmethod
+  def setup_context(ctx, inputs, output):
+    ctx.kw = inputs[1]
+
+  @staticmethod
   def backward(ctx, ct):
+    if ctx.kw.get('version', 'v2') == 'v1':
+      raise NotImplementedError("version='v1' has no column-parallel kernel, hence no transpose rule; use 'v2'")
     kw = dict(ctx.kw, transpose=not ctx.kw['transpose'], outdim_parallel=not ctx.kw['outdim_parallel'])
-    return matvec_raw(contiguous(ct), **kw), None
+    return _Matvec.apply(contiguous(ct), kw), None
+
+  @staticmethod
+  def jvp(ctx, vector_dot, _kw):
+    return None if vector_dot is None else _Matvec.apply(contiguous(vector_dot), ctx.kw)
+
+  @staticmethod
+  def vmap(info, in_dims, vector, kw):
+    return loop_vmap(_Matvec.apply, info, in_dims, (vector, kw))
 
 
 class _EventMatvec(torch.autograd.Function):
-  """The cotangent w.r.t. (floating-point) events is the dense-vector operator with
-  flipped ``transpose`` and ``outdim_parallel`` (event_matvec.py:263-273)."""
+  """Reverse mode: the cotangent w.r.t. (floating-point) events is the dense-vector operator with flipped
+  ``transpose`` and ``outdim_parallel`` (event_matvec.py:263-273).  Forward mode (:242-260): the dense-vector
+  operator on ``events_dot``.  Batching: a loop."""
 
   @staticmethod
-  def forward(ctx, events, kw):
-    ctx.kw = kw
+  def forward(events, kw):
     return event_matvec_raw(events, **kw)
+
+  @staticmethod
+  def setup_context(ctx, inputs, output):
+    ctx.kw = inputs[1]
 
   @staticmethod
   def backward(ctx, ct):
     kw = dict(ctx.kw, transpose=not ctx.kw['transpose'], outdim_parallel=not ctx.kw['outdim_parallel'])
-    return matvec_raw(contiguous(ct), **kw), None
+    return _Matvec.apply(contiguous(ct), kw), None
+
+  @staticmethod
+  def jvp(ctx, events_dot, _kw):
+    return None if events_dot is None else _Matvec.apply(contiguous(events_dot), ctx.kw)
+
+  @staticmethod
+  def vmap(info, in_dims, events, kw):
+    return loop_vmap(_EventMatvec.apply, info, in_dims, (events, kw))
+
+
+class _Matmat(torch.autograd.Function):
+  """The reference registers batching only for the matmat primitives (matmat.py:422,477), no differentiation rule."""
+
+  @staticmethod
+  def forward(matrix, kw):
+    return matmat_raw(matrix, **kw)
+
+  @staticmethod
+  def setup_context(ctx, inputs, output):
+    ctx.set_materialize_grads(False)
+
+  @staticmethod
+  def backward(ctx, ct):
+    raise NotImplementedError('matmat_prob_conn_* has no differentiation rule (none in the reference either)')
+
+  @staticmethod
+  def vmap(info, in_dims, matrix, kw):
+    return loop_vmap(_Matmat.apply, info, in_dims, (matrix, kw))
 
 
 def _check_vector(vector, shape, transpose, what):
@@ -154,11 +199,9 @@ def _matvec(vector, kind, w1, w2, conn_prob, shape, seed, transpose, outdim_para
   kw = dict(kind=kind, w1=w1, w2=w2, conn_prob=conn_prob, shape=(int(shape[0]), int(shape[1])), seed=_seed(seed),
             transpose=bool(transpose), outdim_parallel=bool(outdim_parallel), version=version)
   vector = contiguous(vector)
-  if torch.is_grad_enabled() and vector.requires_grad:
-    if version == 'v1':
-      raise NotImplementedError("version='v1' has no column-parallel kernel, hence no transpose rule; use 'v2'")
-    return _Matvec.apply(vector, kw)
-  return matvec_raw(vector, **kw)
+  if version == 'v1' and torch.is_grad_enabled() and vector.requires_grad:
+    raise NotImplementedError("version='v1' has no column-parallel kernel, hence no transpose rule; use 'v2'")
+  return _Matvec.apply(vector, kw)
 
 
 def event_matvec_v1_raw(event_ids, event_num, *, kind, w1, w2, conn_prob, n_row, n_col, seed, dtype=torch.float32,
@@ -205,10 +248,7 @@ def _event_matvec(events, kind, w1, w2, conn_prob, shape, seed, transpose, outdi
                             bool(transpose), bool(outdim_parallel))
   kw = dict(kind=kind, w1=w1, w2=w2, conn_prob=conn_prob, shape=(int(shape[0]), int(shape[1])), seed=_seed(seed),
             transpose=bool(transpose), outdim_parallel=bool(outdim_parallel))
-  events = contiguous(events)
-  if torch.is_grad_enabled() and events.requires_grad:
-    return _EventMatvec.apply(events, kw)
-  return event_matvec_raw(events, **kw)
+  return _EventMatvec.apply(contiguous(events), kw)
 
 
 def matvec_prob_conn_homo_weight(
@@ -361,8 +401,8 @@ def _matmat(matrix, kind, w1, w2, conn_prob, shape, seed, version, what):
                      f'got {version!r}')
   if not matrix.dtype.is_floating_point:
     matrix = matrix.to(torch.float32)
-  return matmat_raw(contiguous(matrix), kind=kind, w1=w1, w2=w2, conn_prob=conn_prob,
-                    shape=(int(shape[0]), int(shape[1])), seed=int(seed), version=version)
+  return _Matmat.apply(contiguous(matrix), dict(kind=kind, w1=w1, w2=w2, conn_prob=conn_prob,
+                                                shape=(int(shape[0]), int(shape[1])), seed=int(seed), version=version))
 
 
 def matmat_prob_conn_uniform_weight(

@@ -11,7 +11,7 @@ from typing import Tuple, Union
 import torch
 
 from . import _lib, gpu_ops
-from ._checks import as_tensor, contiguous, device_of, float_suffix
+from ._checks import as_tensor, contiguous, device_of, float_suffix, loop_vmap
 
 __all__ = ['csr_matvec', 'cusparse_csr_matvec', 'csr_to_coo', 'coo_to_csr', 'csr_to_dense']
 
@@ -62,16 +62,21 @@ def csr_to_dense(data, indices, indptr, *, shape):
 
 
 class _CSRMatvec(torch.autograd.Function):
-  """Differentiation rules of brainpylib/_src/sparse_ops/cusparse_matvec.py:281-307:
-  w.r.t. the vector the same product with ``not transpose``; w.r.t. homogeneous data
-  ``<ct, op(1, v)>``; w.r.t. heterogeneous data ``v[row] * ct[col]`` if transpose else
-  ``v[col] * ct[row]``."""
+  """Differentiation and batching rules of brainpylib/_src/sparse_ops/cusparse_matvec.py:281-307.
+  Reverse mode: w.r.t. the vector the same product with ``not transpose``; w.r.t. homogeneous data
+  ``<ct, op(1, v)>``; w.r.t. heterogeneous data ``v[row] * ct[col]`` if transpose else ``v[col] * ct[row]``.
+  Forward mode (:281-286): ``op(data_dot, v) + op(data, v_dot)``.  Batching: a loop over the batch."""
 
   @staticmethod
-  def forward(ctx, data, indices, indptr, vector, shape, transpose, method):
-    ctx.save_for_backward(data, indices, indptr, vector)
-    ctx.shape, ctx.transpose = shape, transpose
+  def forward(data, indices, indptr, vector, shape, transpose, method):
     return csr_matvec_raw(data, indices, indptr, vector, shape=shape, transpose=transpose, method=method)
+
+  @staticmethod
+  def setup_context(ctx, inputs, output):
+    data, indices, indptr, vector, shape, transpose, method = inputs
+    ctx.save_for_backward(data, indices, indptr, vector)
+    ctx.save_for_forward(data, indices, indptr, vector)
+    ctx.shape, ctx.transpose, ctx.method = shape, transpose, method
 
   @staticmethod
   def backward(ctx, ct):
@@ -82,14 +87,30 @@ class _CSRMatvec(torch.autograd.Function):
     if ctx.needs_input_grad[0]:
       if data.shape[0] == 1:
         ones = torch.ones(1, dtype=data.dtype, device=data.device)
-        g_data = torch.dot(ct, csr_matvec_raw(ones, indices, indptr, vector, shape=shape,
-                                              transpose=transpose)).reshape(1)
+        g_data = torch.dot(ct, _CSRMatvec.apply(ones, indices, indptr, vector, shape, transpose, 'vector')).reshape(1)
       else:
         row, col = csr_to_coo(indices, indptr)
         g_data = vector[row] * ct[col] if transpose else vector[col] * ct[row]
     if ctx.needs_input_grad[3]:
-      g_vec = csr_matvec_raw(data, indices, indptr, ct, shape=shape, transpose=not transpose)
+      g_vec = _CSRMatvec.apply(data, indices, indptr, ct, shape, not transpose, 'vector')
     return g_data, None, None, g_vec, None, None, None
+
+  # (through `apply`, not the raw kernels: under torch.func transforms tangents arrive wrapped)
+  @staticmethod
+  def jvp(ctx, data_dot, _indices, _indptr, vector_dot, _shape, _transpose, _method):
+    data, indices, indptr, vector = ctx.saved_tensors
+    args = (ctx.shape, ctx.transpose, ctx.method)
+    tangent = None
+    if data_dot is not None:
+      tangent = _CSRMatvec.apply(contiguous(data_dot), indices, indptr, vector, *args)
+    if vector_dot is not None:
+      t = _CSRMatvec.apply(data, indices, indptr, contiguous(vector_dot), *args)
+      tangent = t if tangent is None else tangent + t
+    return tangent
+
+  @staticmethod
+  def vmap(info, in_dims, data, indices, indptr, vector, shape, transpose, method):
+    return loop_vmap(_CSRMatvec.apply, info, in_dims, (data, indices, indptr, vector, shape, transpose, method))
 
 
 def _prepare(data, indices, indptr, vector):
@@ -105,9 +126,7 @@ def _dispatch(data, indices, indptr, vector, shape, transpose, method):
   if indptr.dtype not in (torch.int32, getattr(torch, 'uint32', torch.int32)):
     indptr = indptr.to(torch.int32)
   data, indices, indptr, vector = map(contiguous, (data, indices, indptr, vector))
-  if torch.is_grad_enabled() and (data.requires_grad or vector.requires_grad):
-    return _CSRMatvec.apply(data, indices, indptr, vector, shape, bool(transpose), method)
-  return csr_matvec_raw(data, indices, indptr, vector, shape=shape, transpose=bool(transpose), method=method)
+  return _CSRMatvec.apply(data, indices, indptr, vector, shape, bool(transpose), method)
 
 
 def csr_matvec(

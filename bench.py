@@ -577,7 +577,7 @@ def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb, parts=('in', '
   y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
   y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
   name = 'event_cbcsr_matvec_heter_float_float'
-  opaque = event_ops._cb_descriptor(shape[0], shape[1], cb.block_width, cb.scale_log2)
+  opaque = event_ops._cb_descriptor(shape[0], shape[1], cb.block_width, cb.scale_log2, cb.team_lanes_log2)
   ws = [torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device) for _ in range(n_buf)]
   target = _lib.target(name)
   bufs = [(ctypes.c_void_p * 5)(cb.groups.data_ptr(), cb.offsets.data_ptr(), ev_buf[b].data_ptr(), y_buf[b].data_ptr(),

@@ -17,12 +17,14 @@
 // active rows; its 32 warps split those rows and run independently of one another (no barrier in the
 // main loop, no wait on another warp).  A warp resolves 32 of its rows at a time, one per lane (spike
 // list -> row -> segment of this block), with the next 32 already in flight, and then streams the
-// segments through a private ring of small shared-memory buffers: teams of four lanes copy one segment
-// each with 16-byte `cp.async` (eight segments per round, packed back to back), the round is committed
-// as one group, and while it is in flight the warp adds the oldest buffer into the slice: one lane per
-// group of 8 synapses, one shared-memory atomic per synapse.  A buffer is walked as a plain array of
-// groups (no segment boundaries are needed: padding is harmless).  At the end the P slices of a block
-// are added into the zero-filled y with 16-byte vector reductions.
+// segments through a private ring of small shared-memory buffers.  A buffer has 32 slots of one group;
+// a team of L lanes (L = 4, 8, 16 or 32, chosen from the mean segment length when the matrix is
+// prepared) owns L consecutive slots and copies up to L groups of ONE segment into them with 16-byte
+// `cp.async`, so a round moves 32 / L segments and needs no packing: where a piece lands is fixed.  The
+// round is committed as one group, and while it is in flight the warp adds the oldest buffer into the
+// slice: lane l takes slot l (if its team filled it), one shared-memory atomic per synapse.  A segment
+// longer than L groups simply stays at the head of the queue for another round.  At the end the P
+// slices of a block are added into the zero-filled y with 16-byte vector reductions.
 //
 // Measured alternatives that lost (1e6 x 1e6, 1000 synapses per row, 1 % of the rows active, 37 blocks):
 // one producer warp feeding the others with one `cp.async.bulk` per segment: 4x slower (a segment is
@@ -30,7 +32,8 @@
 // into registers: 2x slower (every lane of a load instruction touches a different sector); a ticketed
 // combine of the P slices through a scratch area instead of the reductions: 5 us slower; a deeper or
 // shallower ring: no change, the loop is bound by the instructions it issues per round, not by memory
-// latency.
+// latency; pieces packed back to back (a prefix sum over the teams per round) instead of fixed slots:
+// about twice the instructions per row.
 //
 // FIXED = false: float accumulators.  A float add on shared memory is a compare-and-swap loop on this
 // hardware (about 3.4 per clock per SM at random addresses, each a chain of dependent instructions).
@@ -51,20 +54,19 @@ namespace {
 constexpr int CB_THREADS = 1024;
 constexpr int CB_WARPS = CB_THREADS / 32;
 constexpr uint32_t CB_GROUP_BYTES = 48;
-constexpr uint32_t CB_MAX_WIDTH = 45056;           // 176 KB of shared memory for the slice, the rest for the ring
+constexpr uint32_t CB_MAX_WIDTH = 32256;           // 126 KB of shared memory for the slice, the rest for two ring buffers per warp
 constexpr uint32_t CB_MAX_BLOCKS = 1024;
 // static shared memory of a kernel that calls cb_scatter_body (prefix, warp totals), rounded up
 constexpr uint32_t CB_STATIC_SMEM = 4608;
 constexpr uint32_t CB_SMEM_LIMIT = 232448 - CB_STATIC_SMEM;           // 227 KB per CTA on sm_100
 
-constexpr uint32_t CB_MAX_BUF_GROUPS = 32;         // groups per ring buffer: one per lane when it is accumulated
-constexpr uint32_t CB_MIN_BUF_GROUPS = 8;
+constexpr uint32_t CB_BUF_GROUPS = 32;             // slots per ring buffer: one per lane
+constexpr uint32_t CB_BUF_BYTES = CB_BUF_GROUPS * CB_GROUP_BYTES;   // 1536
 
 // ---- shared-memory layout, computed on the host and passed to the kernel ----
-//   acc [acc_bytes]   then per warp a ring of n_buf buffers of buf_groups * 48 bytes
+//   acc [acc_bytes]   then per warp a ring of n_buf buffers of 32 groups
 struct CbPlan {
     uint32_t n_buf;        // 3 or 2 ring buffers per warp
-    uint32_t buf_groups;   // groups per buffer
     uint32_t acc_bytes;    // slice of y, rounded up to 16 bytes
     uint32_t smem_bytes;   // dynamic shared memory of the launch
     bool ok;
@@ -75,18 +77,9 @@ inline CbPlan cb_plan(uint32_t width, uint32_t extra_bytes = 0) {
     p.acc_bytes = (width * 4u + 15u) & ~15u;
     const uint32_t limit = CB_SMEM_LIMIT - extra_bytes;
     p.ok = false;
-    if (p.acc_bytes + CB_WARPS * 2u * CB_MIN_BUF_GROUPS * CB_GROUP_BYTES > limit) return p;
-    const uint32_t ring = limit - p.acc_bytes;
-    // three full buffers per warp when they fit, else two buffers as large as fit
-    if (ring >= CB_WARPS * 3u * CB_MAX_BUF_GROUPS * CB_GROUP_BYTES) {
-        p.n_buf = 3;
-        p.buf_groups = CB_MAX_BUF_GROUPS;
-    } else {
-        p.n_buf = 2;
-        const uint32_t g = ring / (CB_WARPS * 2u * CB_GROUP_BYTES);
-        p.buf_groups = g > CB_MAX_BUF_GROUPS ? CB_MAX_BUF_GROUPS : g;
-    }
-    p.smem_bytes = p.acc_bytes + CB_WARPS * p.n_buf * p.buf_groups * CB_GROUP_BYTES;
+    if (p.acc_bytes + CB_WARPS * 2u * CB_BUF_BYTES > limit) return p;
+    p.n_buf = (p.acc_bytes + CB_WARPS * 3u * CB_BUF_BYTES <= limit) ? 3u : 2u;
+    p.smem_bytes = p.acc_bytes + CB_WARPS * p.n_buf * CB_BUF_BYTES;
     p.ok = true;
     return p;
 }
@@ -132,16 +125,47 @@ __device__ __forceinline__ void cb_add_group(float *acc, const CbGroup &g) {
     cb_add<FIXED>(acc, g.cc.w >> 16, g.wb.w);
 }
 
-// One warp adds the `n` groups of a ring buffer into the slice: one lane per group.
+// Lane `lane` adds the group in its slot of a ring buffer into the slice (when its team filled that slot).
 template<bool FIXED>
-__device__ __forceinline__ void cb_accumulate(float *acc, const unsigned char *buf, const uint32_t n, const uint32_t lane) {
-    for (uint32_t g = lane; g < n; g += 32u) {
+__device__ __forceinline__ void cb_accumulate(float *acc, const unsigned char *buf, const bool filled, const uint32_t lane) {
+    if (filled) {
         CbGroup grp;
-        grp.wa = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES);
-        grp.wb = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES + 16);
-        grp.cc = *reinterpret_cast<const uint4 *>(buf + g * CB_GROUP_BYTES + 32);
+        grp.wa = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES);
+        grp.wb = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 16);
+        grp.cc = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 32);
         cb_add_group<FIXED>(acc, grp);
     }
+}
+
+// Exclusive prefix over the chunk counts for a block of 1024 threads (one count per thread): prefix[k] for k < 1024,
+// prefix[1024] = total; returns the total.  `warp_total`: shared, 32 words.
+__device__ __forceinline__ uint32_t cb_chunk_prefix(const uint32_t *__restrict__ counts, const uint32_t n_chunks,
+                                                    uint32_t *prefix, uint32_t *warp_total) {
+    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t c = t < n_chunks ? counts[t] : 0u;
+    uint32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(FULL_MASK, incl, o);
+        if (lane >= static_cast<uint32_t>(o)) incl += v;
+    }
+    if (lane == 31) warp_total[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t w = warp_total[lane];
+        uint32_t wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(FULL_MASK, wi, o);
+            if (lane >= static_cast<uint32_t>(o)) wi += v;
+        }
+        warp_total[lane] = wi - w;
+        if (lane == 31) prefix[MAX_CHUNKS] = wi;
+    }
+    __syncthreads();
+    prefix[t] = warp_total[warp] + incl - c;
+    __syncthreads();
+    return prefix[MAX_CHUNKS];
 }
 
 // Optional phase stamps (nanoseconds of %globaltimer), 8 words per CTA, written when `trace` is not null:
@@ -160,19 +184,19 @@ __device__ __forceinline__ void cb_stamp(unsigned long long *trace, const uint32
 //   counts / ids: the spike list (chunk_prefix / list_row layout); y: this matrix's output, already zero.
 //   smem: dynamic shared memory laid out by cb_plan; prefix / warp_total: static shared memory.
 //   inv_scale: FIXED only, 2^-k.
-template<int NBUF, bool FIXED>
+template<int NBUF, bool FIXED, int LOG_L>
 __device__ __forceinline__ void
 cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets, const uint32_t n_col,
                 const uint32_t width, const uint32_t n_blocks, const uint32_t b, const uint32_t p, const uint32_t P,
                 const uint32_t chunk, const uint32_t n_chunks, const uint32_t *__restrict__ counts,
-                const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t buf_groups,
-                const uint32_t acc_bytes, unsigned char *smem, uint32_t *prefix, uint32_t *warp_total,
-                const float inv_scale, unsigned long long *trace = nullptr, const uint32_t trace_cta = 0) {
+                const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t acc_bytes,
+                unsigned char *smem, uint32_t *prefix, uint32_t *warp_total, const float inv_scale,
+                unsigned long long *trace = nullptr, const uint32_t trace_cta = 0) {
+    constexpr uint32_t L = 1u << LOG_L, TEAMS = 32u / L;          // lanes (= slots) per team, teams per warp
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t team = lane >> 2, sub = lane & 3u;
-    const uint32_t buf_bytes = buf_groups * CB_GROUP_BYTES;
+    const uint32_t team = lane >> LOG_L, sub = lane & (L - 1u);
     float *acc = reinterpret_cast<float *>(smem);
-    unsigned char *ring = smem + acc_bytes + warp * (NBUF * buf_bytes);
+    unsigned char *ring = smem + acc_bytes + warp * (NBUF * CB_BUF_BYTES);
     const uint32_t col0 = b * width;
     const uint32_t my_width = min(width, n_col - col0);
     if (threadIdx.x == 0) {
@@ -184,7 +208,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     }
     for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = 0.0f;
 
-    const uint32_t n_act = chunk_prefix(counts, n_chunks, prefix, warp_total);   // ends with a barrier
+    const uint32_t n_act = cb_chunk_prefix(counts, n_chunks, prefix, warp_total);   // ends with a barrier
     if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 1);
     const uint32_t mine = n_act > p ? (n_act - p + P - 1) / P : 0;               // the CTA's rows: p, p + P, ...
     const uint32_t K = mine > warp ? (mine - warp + 31u) / 32u : 0u;             // this warp's: warp, warp + 32, ... of those
@@ -206,47 +230,43 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     resolve(lane, next_src, next_rem);
     if (trace != nullptr && threadIdx.x == 0 && next_rem != 0xffffffffu) cb_stamp(trace, trace_cta, 2);
     uint32_t issued = 0, consumed = 0;     // rounds committed / accumulated; buffer of round r is r % NBUF
-    uint32_t filled = 0;                   // groups in the buffers of the rounds in flight, 8 bits each, oldest lowest
+    uint32_t pieces = 0;                   // groups this lane's team copied in the rounds in flight, 8 bits each, oldest lowest
 
     for (uint32_t k0 = 0; k0 < K; k0 += 32u) {
         uint32_t src = next_src, rem = next_rem;
         resolve(k0 + 32u + lane, next_src, next_rem);      // in flight while this batch streams
         uint32_t mask = __ballot_sync(FULL_MASK, rem > 0);
         while (mask) {
-            // one round: team t copies (a piece of) the segment held by lane first + t, packed in lane order
+            // one round: team t copies up to L groups of the segment held by lane first + t into its own slots
             const uint32_t first = __ffs(mask) - 1u;
             const uint32_t owner = first + team;
             const uint32_t o_src = __shfl_sync(FULL_MASK, src, owner & 31u);
             uint32_t o_rem = __shfl_sync(FULL_MASK, rem, owner & 31u);
             if (owner > 31u) o_rem = 0;
-            uint32_t incl = o_rem;                          // inclusive prefix over the teams (lanes of a team agree)
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(FULL_MASK, incl, o);
-                if (lane >= static_cast<uint32_t>(o)) incl += t;
-            }
-            const uint32_t excl = incl - o_rem;
-            const uint32_t piece = excl < buf_groups ? min(o_rem, buf_groups - excl) : 0u;
-            const uint32_t round_groups = min(__shfl_sync(FULL_MASK, incl, 31), buf_groups);
-            unsigned char *dst = ring + (issued % NBUF) * buf_bytes + excl * CB_GROUP_BYTES;
+            const uint32_t piece = min(o_rem, L);
+            unsigned char *dst = ring + (issued % NBUF) * CB_BUF_BYTES + team * (L * CB_GROUP_BYTES);
             const unsigned char *from = groups + static_cast<uint64_t>(o_src) * CB_GROUP_BYTES;
-            for (uint32_t c = sub; c < 3u * piece; c += 4u) cp_async16(dst + c * 16u, from + c * 16u);
+#pragma unroll
+            for (uint32_t it = 0; it < 3u; ++it) {         // a group is three 16-byte chunks: 3 * piece <= 3 L chunks
+                const uint32_t c = sub + it * L;
+                if (c < 3u * piece) cp_async16(dst + c * 16u, from + c * 16u);
+            }
             cp_async_commit();
             // the lanes that hold the segments just copied move on
             const uint32_t my_rank = lane - first;
-            const uint32_t taken = __shfl_sync(FULL_MASK, piece, (my_rank & 7u) * 4u);
-            if (lane >= first && my_rank < 8u) {
+            const uint32_t taken = __shfl_sync(FULL_MASK, piece, (my_rank & (TEAMS - 1u)) << LOG_L);
+            if (lane >= first && my_rank < TEAMS) {
                 src += taken;
                 rem -= taken;
             }
-            filled |= round_groups << (8u * (issued - consumed));
+            pieces |= piece << (8u * (issued - consumed));
             ++issued;
             if (issued - consumed == NBUF) {                // ring full: accumulate the oldest round
                 cp_async_wait<NBUF - 1>();
                 __syncwarp();
-                cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * buf_bytes, filled & 0xffu, lane);
+                cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane);
                 __syncwarp();
-                filled >>= 8;
+                pieces >>= 8;
                 ++consumed;
             }
             mask = __ballot_sync(FULL_MASK, rem > 0);
@@ -255,8 +275,8 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     cp_async_wait<0>();
     __syncwarp();
     while (consumed < issued) {
-        cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * buf_bytes, filled & 0xffu, lane);
-        filled >>= 8;
+        cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane);
+        pieces >>= 8;
         ++consumed;
     }
     if (trace != nullptr && lane == 0) {

@@ -222,7 +222,7 @@ cb_max_kernel(const float *__restrict__ colsum, const uint32_t n, uint32_t *__re
 
 bool build_arguments_ok(uint32_t col_lo, uint32_t col_hi, uint32_t width, uint32_t *n_blocks) {
     if (col_hi < col_lo || width == 0 || width > CB_MAX_WIDTH || (width & 31u) != 0) {
-        set_status(BPL_ERR_ARGUMENT, "column-blocked build: block_width must be a multiple of 32 in 32..45056 "
+        set_status(BPL_ERR_ARGUMENT, "column-blocked build: block_width must be a multiple of 32 in 32..32256 "
                                      "and col_lo <= col_hi");
         return false;
     }

@@ -8,8 +8,10 @@
 // builder.
 //
 //   event_cbcsr_matvec_heter_float_{bool,float}
-//   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2}   (bpl_build_cbcsr_descriptor)
-//           fixed_point = 0: float accumulators; 1: 32-bit fixed point with 2^scale_log2 units per 1.0
+//   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2, u32 team_lanes_log2}
+//           (bpl_build_cbcsr_descriptor).  fixed_point = 0: float accumulators; 1: 32-bit fixed point with
+//           2^scale_log2 units per 1.0.  team_lanes_log2 = 2..5: a (row, block) segment is copied by 4, 8, 16 or 32
+//           lanes, up to that many groups per round; pick the smallest that covers most segments.
 //   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
 //   workspace: as for event_csr_matvec with transpose (4 KB + 4 B per row): the compacted spike list
 #include <type_traits>
@@ -28,25 +30,43 @@ struct TripleSizeDescriptor {   // same layout as the reference's (lib/kernel_he
 struct CbDescriptor {
     unsigned int n_row, n_col, block_width;
     int fixed_point, scale_log2;
+    unsigned int team_lanes_log2;   // 2..5: lanes (and groups per round) a segment gets; 0 = 2
 };
-static_assert(sizeof(CbDescriptor) == 20, "layout");
+static_assert(sizeof(CbDescriptor) == 24, "layout");
 
 // Optional phase stamps of the next launches made by this host thread (see cb_stamp): 8 words per CTA.
 thread_local unsigned long long *g_cb_trace = nullptr;
 
-template<int NBUF, bool FIXED>
+template<int NBUF, bool FIXED, int LOG_L>
 __global__ void __launch_bounds__(CB_THREADS, 1)
 event_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets,
                         const uint32_t n_col, const uint32_t width, const uint32_t n_blocks, const uint32_t P,
                         const uint32_t chunk, const uint32_t n_chunks, const uint32_t *__restrict__ counts,
-                        const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t buf_groups,
-                        const uint32_t acc_bytes, const float inv_scale, unsigned long long *__restrict__ trace) {
+                        const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t acc_bytes,
+                        const float inv_scale, unsigned long long *__restrict__ trace) {
     extern __shared__ __align__(128) unsigned char cb_smem[];
     __shared__ uint32_t prefix[MAX_CHUNKS + 1];
     __shared__ uint32_t warp_total[CB_WARPS];
-    cb_scatter_body<NBUF, FIXED>(groups, offsets, n_col, width, n_blocks, blockIdx.x / P, blockIdx.x % P, P, chunk,
-                                 n_chunks, counts, ids, y, buf_groups, acc_bytes, cb_smem, prefix, warp_total, inv_scale,
-                                 trace, blockIdx.x);
+    cb_scatter_body<NBUF, FIXED, LOG_L>(groups, offsets, n_col, width, n_blocks, blockIdx.x / P, blockIdx.x % P, P, chunk,
+                                        n_chunks, counts, ids, y, acc_bytes, cb_smem, prefix, warp_total, inv_scale, trace,
+                                        blockIdx.x);
+}
+
+using CbKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
+                          const uint32_t *, const uint32_t *, float *, uint32_t, float, unsigned long long *);
+
+template<int NBUF, bool FIXED>
+CbKernel cb_kernel_for_lanes(uint32_t log_l) {
+    switch (log_l) {
+        case 3: return event_cb_scatter_kernel<NBUF, FIXED, 3>;
+        case 4: return event_cb_scatter_kernel<NBUF, FIXED, 4>;
+        case 5: return event_cb_scatter_kernel<NBUF, FIXED, 5>;
+        default: return event_cb_scatter_kernel<NBUF, FIXED, 2>;
+    }
+}
+CbKernel cb_kernel(uint32_t n_buf, bool fixed, uint32_t log_l) {
+    if (n_buf == 3) return fixed ? cb_kernel_for_lanes<3, true>(log_l) : cb_kernel_for_lanes<3, false>(log_l);
+    return fixed ? cb_kernel_for_lanes<2, true>(log_l) : cb_kernel_for_lanes<2, false>(log_l);
 }
 
 bool cb_kernel_configured() {
@@ -54,15 +74,14 @@ bool cb_kernel_configured() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_device != dev) {
-        const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-        const int limit = static_cast<int>(CB_SMEM_LIMIT);
-        if (cudaFuncSetAttribute(event_cb_scatter_kernel<2, false>, attr, limit) != cudaSuccess ||
-            cudaFuncSetAttribute(event_cb_scatter_kernel<3, false>, attr, limit) != cudaSuccess ||
-            cudaFuncSetAttribute(event_cb_scatter_kernel<2, true>, attr, limit) != cudaSuccess ||
-            cudaFuncSetAttribute(event_cb_scatter_kernel<3, true>, attr, limit) != cudaSuccess) {
-            launch_ok();
-            return false;
-        }
+        for (uint32_t n_buf = 2; n_buf <= 3; ++n_buf)
+            for (int fixed = 0; fixed < 2; ++fixed)
+                for (uint32_t log_l = 2; log_l <= 5; ++log_l)
+                    if (cudaFuncSetAttribute(cb_kernel(n_buf, fixed != 0, log_l), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(CB_SMEM_LIMIT)) != cudaSuccess) {
+                        launch_ok();
+                        return false;
+                    }
         configured_device = dev;
     }
     return true;
@@ -88,7 +107,11 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     }
     const float inv_scale = d->fixed_point ? ldexpf(1.0f, -d->scale_log2) : 1.0f;
     if (width == 0 || width > CB_MAX_WIDTH || (width & 31u) != 0) {
-        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width must be a multiple of 32 in 32..45056");
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width must be a multiple of 32 in 32..32256");
+        return;
+    }
+    if (d->team_lanes_log2 != 0 && (d->team_lanes_log2 < 2 || d->team_lanes_log2 > 5)) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: team_lanes_log2 must be 2..5");
         return;
     }
     if (n_col == 0) return;
@@ -129,14 +152,11 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
         set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width leaves no shared memory for the copy buffers");
         return;
     }
+    const uint32_t log_l = d->team_lanes_log2 == 0 ? 2u : d->team_lanes_log2;
     if (profile_before()) cudaEventRecord(profile_before(), stream);
-#define BPL_CB_LAUNCH(NBUF, FIXED)                                                                              \
-    event_cb_scatter_kernel<NBUF, FIXED><<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(                 \
-        groups, offsets, n_col, width, n_blocks, P, p.chunk, p.n_chunks, counts, ids, y, plan.buf_groups,        \
-        plan.acc_bytes, inv_scale, g_cb_trace)
-    if (d->fixed_point) { if (plan.n_buf == 3) BPL_CB_LAUNCH(3, true); else BPL_CB_LAUNCH(2, true); }
-    else                { if (plan.n_buf == 3) BPL_CB_LAUNCH(3, false); else BPL_CB_LAUNCH(2, false); }
-#undef BPL_CB_LAUNCH
+    cb_kernel(plan.n_buf, d->fixed_point != 0, log_l)<<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(
+        groups, offsets, n_col, width, n_blocks, P, p.chunk, p.n_chunks, counts, ids, y, plan.acc_bytes, inv_scale,
+        g_cb_trace);
     if (profile_after()) cudaEventRecord(profile_after(), stream);
     launch_ok();
 }
@@ -166,9 +186,9 @@ void event_cbcsr_matvec_list_heter_float(bpl_stream_t s, void **b, const char *o
 void bpl_cbcsr_trace(void *buffer) { g_cb_trace = static_cast<unsigned long long *>(buffer); }
 
 size_t bpl_build_cbcsr_descriptor(uint32_t n_row, uint32_t n_col, uint32_t block_width, int fixed_point,
-                                  int scale_log2, void *out, size_t cap) {
+                                  int scale_log2, uint32_t team_lanes_log2, void *out, size_t cap) {
     if (out == nullptr || cap < sizeof(CbDescriptor)) return 0;
-    const CbDescriptor d{n_row, n_col, block_width, fixed_point, scale_log2};
+    const CbDescriptor d{n_row, n_col, block_width, fixed_point, scale_log2, team_lanes_log2};
     __builtin_memcpy(out, &d, sizeof(d));
     return sizeof(d);
 }

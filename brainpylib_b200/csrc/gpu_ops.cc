@@ -106,7 +106,7 @@ size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t o
         return bpl_event_csr_workspace_bytes(d->uint_x, d->bool_x ? 1 : 0);
     }
     if (std::strncmp(target_name, "event_cbcsr_matvec_", 19) == 0) {
-        if (opaque == nullptr || opaque_len != 20) return 0;
+        if (opaque == nullptr || opaque_len != 24) return 0;
         return bpl_event_csr_workspace_bytes(*reinterpret_cast<const uint32_t *>(opaque), 1);
     }
     if (std::strncmp(target_name, "nonzero_", 8) == 0) {

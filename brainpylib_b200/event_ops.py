@@ -262,7 +262,7 @@ def event_info(events: torch.Tensor):
 # GPU (csrc/cbcsr_build.cu); the operator that consumes the format is stateless.
 
 CB_GROUP_BYTES = 48
-CB_MAX_WIDTH = 45056
+CB_MAX_WIDTH = 32256
 
 
 class ColumnBlockedCSR:
@@ -275,6 +275,11 @@ class ColumnBlockedCSR:
 
   def __init__(self, groups, offsets, shape, block_width, col_range=None, nse=None, scale_log2=None):
     self.groups, self.offsets = groups, offsets
+    # lanes (= records per round) one (row, block) segment gets in the kernel: the smallest of 4, 8, 16, 32 that
+    # covers an average segment with some room (longer segments take more rounds)
+    segments = max(1, int(offsets.shape[0]) * max(1, int(offsets.shape[1]) - 1))
+    mean_groups = (groups.numel() // CB_GROUP_BYTES) / segments
+    self.team_lanes_log2 = 2 if mean_groups <= 3.6 else 3 if mean_groups <= 7.0 else 4 if mean_groups <= 14.0 else 5
     self.scale_log2 = scale_log2     # None: float accumulators; k: 32-bit fixed point, 2^k units per 1.0
     self.shape = (int(shape[0]), int(shape[1]))
     self.block_width = int(block_width)
@@ -418,7 +423,7 @@ def event_cbcsr_matvec_raw(blocked: ColumnBlockedCSR, events, *, out=None, works
     raise ValueError('events must be bool or float32')
   if events.device.type != 'cuda':
     raise GPUOperatorNotFound(f'{name} (operands are on {events.device}, a CUDA device is required)')
-  opaque = _cb_descriptor(n_row, n_col, blocked.block_width, blocked.scale_log2)
+  opaque = _cb_descriptor(n_row, n_col, blocked.block_width, blocked.scale_log2, blocked.team_lanes_log2)
   if out is None:
     out = torch.empty(n_col, dtype=torch.float32, device=events.device)
   if workspace is None:
@@ -427,10 +432,10 @@ def event_cbcsr_matvec_raw(blocked: ColumnBlockedCSR, events, *, out=None, works
   return out
 
 
-def _cb_descriptor(n_row, n_col, block_width, scale_log2=None):
+def _cb_descriptor(n_row, n_col, block_width, scale_log2=None, team_lanes_log2=2):
   import struct
-  return struct.pack('<IIIii', n_row, n_col, block_width, 0 if scale_log2 is None else 1,
-                     0 if scale_log2 is None else int(scale_log2))
+  return struct.pack('<IIIiiI', n_row, n_col, block_width, 0 if scale_log2 is None else 1,
+                     0 if scale_log2 is None else int(scale_log2), int(team_lanes_log2))
 
 
 def event_cbcsr_matvec(blocked: ColumnBlockedCSR, events: torch.Tensor) -> torch.Tensor:

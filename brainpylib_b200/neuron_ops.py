@@ -116,7 +116,7 @@ def event_csr_matvec_from_list(data, indices, indptr, spike_list, y, *, shape, p
   if prepared is not None:
     if not isinstance(prepared, ColumnBlockedCSR) or prepared.shape != (n_row, n_col):
       raise ValueError('prepared does not describe a matrix of this shape')
-    opaque = _cb_descriptor(n_row, n_col, prepared.block_width, prepared.scale_log2)
+    opaque = _cb_descriptor(n_row, n_col, prepared.block_width, prepared.scale_log2, prepared.team_lanes_log2)
     _lib.call('event_cbcsr_matvec_list_heter_float', [prepared.groups, prepared.offsets, spike_list, y], opaque,
               device=y.device)
     return y

@@ -75,7 +75,7 @@ size_t bpl_build_lif_exp_descriptor(uint32_t n, uint32_t n_channels, float t, co
                                     float ext_input, float V_rest, float V_th, float V_reset, float R, float lif_decay,
                                     float tau_ref, void *out, size_t cap);
 size_t bpl_build_cbcsr_descriptor(uint32_t n_row, uint32_t n_col, uint32_t block_width, int fixed_point,
-                                  int scale_log2, void *out, size_t cap);
+                                  int scale_log2, uint32_t team_lanes_log2, void *out, size_t cap);
 
 /* ---- workspace -------------------------------------------------------------------------
  * Bytes of the trailing workspace buffer a target needs for the given opaque descriptor
@@ -103,13 +103,14 @@ void bpl_profile_scatter_events(void *before, void *after);
  *
  * event_cbcsr_matvec_heter_float_{bool,float}   (no counterpart in the reference)
  *   y = A^T events on a COLUMN-BLOCKED matrix built once by bpl_cbcsr_plan / bpl_cbcsr_fill (below): the
- *   post-synaptic neurons are cut into blocks of `block_width` columns (a multiple of 32, <= 45056); the
+ *   post-synaptic neurons are cut into blocks of `block_width` columns (a multiple of 32, <= 32256); the
  *   matrix stays row-major, the synapses of a row are grouped by block and stored in records of 8
  *   (8 x float32 weight - or int32 round(w * 2^k) for fixed-point matrices - then 8 x uint16 column offset
  *   into the block; a segment is padded with zero-weight synapses to whole records); offsets[row][b] ..
  *   offsets[row][b + 1] are the records of row's segment for block b.  One block's slice of y is accumulated
  *   in shared memory, which lifts the scattered-reduction limit of the plain CSR scatter.
- *   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2} (bpl_build_cbcsr_descriptor)
+ *   opaque  {u32 n_row, u32 n_col, u32 block_width, i32 fixed_point, i32 scale_log2, u32 team_lanes_log2}
+ *           (bpl_build_cbcsr_descriptor; team_lanes_log2 2..5: lanes and groups per round a segment gets)
  *   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
  *   workspace: bpl_workspace_bytes() (as for event_csr_matvec with transpose)
  *

@@ -20,7 +20,7 @@ def _dense(data, indices, indptr, shape, lo, hi):
 
 
 @pytest.mark.parametrize('shape,block_width,col_range', [((40, 100), 32, None), ((64, 700), 256, None),
-                                                         ((30, 66000), 45056, None), ((5, 7), 32, None),
+                                                         ((30, 66000), 32256, None), ((5, 7), 32, None),
                                                          ((50, 1000), 64, (250, 500)), ((50, 1000), 96, (990, 1000))])
 def test_layout_model_keeps_every_synapse_in_its_row_and_block(shape, block_width, col_range):
   data, indices, indptr, _ = cases.csr_case(shape, 0.2 if shape[1] < 2000 else 0.002, 91)
@@ -45,7 +45,7 @@ def test_layout_model_ragged_rows_duplicates_and_padding():
   assert int(offsets[0, -1] - offsets[0, 0]) == 0
 
 
-@pytest.mark.parametrize('width', [0, 31, 33, 1000 + 1, 45056 + 32, 70000])
+@pytest.mark.parametrize('width', [0, 31, 33, 1000 + 1, 32256 + 32, 70000])
 def test_block_widths_the_kernel_cannot_take_are_refused(width):
   with pytest.raises(ValueError):
     event_ops.check_block_width(width)

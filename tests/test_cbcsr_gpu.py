@@ -67,14 +67,14 @@ def test_cbcsr_long_segments_duplicates_and_ragged_rows(cuda):
   check(cuda, data, indices, indptr, (lens.shape[0], 300), evs)
 
 
-def test_cbcsr_more_active_rows_than_one_pass_resolves(cuda):
-  """70000 active rows over 2 column blocks = 16 CTA shares of 4375 rows: more than the 4096 rows a CTA resolves per
-  pass, so the ring has to carry on over a second pass."""
+def test_cbcsr_widest_block_and_many_rows_per_warp(cuda):
+  """70000 active rows over 2 column blocks of the largest width = 16 CTA shares of 4375 rows: every warp walks several
+  batches of 32 rows with only two ring buffers (the slice takes most of the shared memory)."""
   shape = (70000, 40000)
   rng = np.random.default_rng(84)
   lens = rng.integers(10, 30, shape[0])
   data, indices, indptr, rng = cases.ragged_csr(lens, shape[1], 84)
-  check(cuda, data, indices, indptr, shape, [np.ones(shape[0], dtype=bool)], block_width=32768, compare_layout=False)
+  check(cuda, data, indices, indptr, shape, [np.ones(shape[0], dtype=bool)], block_width=32256, compare_layout=False)
 
 
 def test_cbcsr_homogeneous_weight_and_column_range(cuda):

@@ -18,9 +18,9 @@ prepared once into the column-blocked layout (float32 accumulation), K steps in 
 resident in HBM, CUDA events.  `stateless_csr` is the same operator without the prepared matrix (the
 reference's exact signature), `prepared_fixed_point` the prepared matrix with fixed-point accumulation.
 `roofline` is for the dominant kernel of `value` alone (CUDA events recorded around it by the library's
-profiling hook).  `e2e` drives the C-ABI target with HOST buffers: every step copies that step's spikes
-from pinned host memory and the result back, three streams, the K steps captured in one graph.
-N > 1 GPUs.  The matrix is sharded by post-synaptic neuron (plain CSR shards), every rank owns 1/N of the
+profiling hook).  `e2e` drives the C-ABI target with HOST buffers (`HostSteps`, `bpl_run_host_steps`): every step
+copies that step's spikes from pinned host memory and the result back, three streams, enqueued by native code.
+N > 1 GPUs.  The matrix is sharded by post-synaptic neuron (each shard prepared like the 1-GPU matrix), every rank owns 1/N of the
 spike sources, one launch per step pushes the next step's spike list to the peers and scatters this
 step's; `e2e` moves only the rank's own n/N spikes in and its own slice of the result out.
 `cpu_baseline` / `--impl reference` time the reference's own CPU kernel (lib/cpu_event_sum.cc compiled
@@ -50,6 +50,25 @@ WORKLOAD = 'C3 event_csr_matvec transpose=True: 1e6 neurons x 1000 synapses (1e9
 
 def log(*a):
   print(*a, file=sys.stderr, flush=True)
+
+
+_RESULT_OUT = None
+
+
+def keep_stdout_for_the_result():
+  """Libraries loaded later (NCCL's version banner) write to file descriptor 1: point it at stderr and keep the
+  original for the one JSON line."""
+  global _RESULT_OUT
+  if _RESULT_OUT is None:
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), 'w')
+    os.dup2(2, 1)
+
+
+def emit(line):
+  out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+  out.write(json.dumps(line) + '\n')
+  out.flush()
 
 
 def measured_peaks():
@@ -253,7 +272,7 @@ def run_reference(args):
     'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
     'gpu_launches': 0,
   }
-  print(json.dumps(line), flush=True)
+  emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -428,7 +447,8 @@ def run_single(args, torch, device):
                'sharding': 'none'},
     'e2e': {'value': total_ops / (e2e['ms'] * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'],
             'd2h_bytes_per_step': e2e['d2h'], 'ms_per_step': e2e['ms'] / K,
-            'path': 'C-ABI target event_cbcsr_matvec_heter_float_float, pinned host spikes in, pinned host result out'},
+            'path': 'brainpylib_b200.HostSteps.run -> bpl_run_host_steps -> C-ABI target event_cbcsr_matvec_heter_float_float: '
+                    'pinned host spikes in, pinned host result out, every step'},
     'gpu_launches': 2 * K,     # spike scan + scatter per step
     'roofline': roof('event_cb_scatter_kernel<float accumulate>', cb_kernel_bytes, k_ms, cb_step_bytes, ms,
                      padded * 6.0 * n_act * DEGREE / cb_kernel_bytes,
@@ -456,7 +476,7 @@ def run_single(args, torch, device):
                             'sample': f'{done} steps ({seconds:.1f} s of CPU time) on {CPU_SAMPLE}; '
                                       'lib/cpu_event_sum.cc serial C++',
                             'host_cores_available': os.cpu_count()}
-  print(json.dumps(line), flush=True)
+  emit(line)
 
 
 def caller_fusion(torch, device, side, prepared, shape, K):
@@ -551,93 +571,32 @@ def reference_cuda_c3(torch, work, ev_dev, shape, first, count, ops_per_step):
           'one atomicAdd per synapse), host-launched back to back, CUDA events on the legacy default stream'}
 
 
-def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb, parts=('in', 'compute', 'out')):
-  """End to end through the C ABI with HOST buffers: every step copies that step's spike vector from pinned
-  host memory to the device, calls the custom-call target on the prepared matrix and copies the result back
-  to pinned host memory.  Three streams (copy in, compute, copy out) and triple buffers, so step s + 1's
-  spikes are copied in while step s computes and step s - 1's result is copied out.  The CUDA runtime is
-  driven directly (ctypes) so that Python dispatch stays off the critical path.  (Capturing the same steps in
-  a CUDA graph was measured too: the 4 MB copies no longer overlapped and a step took 130 us instead of ~90.)"""
-  import ctypes
-  from brainpylib_b200 import _lib, event_ops
-  rt = ctypes.CDLL('libcudart.so.12')
-  rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
-  rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint]
-  rt.cudaEventRecord.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
-  rt.cudaStreamWaitEvent.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
-
-  def check(code):
-    if code != 0:
-      raise SystemExit(f'CUDA runtime call failed with error {code}')
-
-  streams = [torch.cuda.Stream(device) for _ in range(3)]
-  s_in, s_c, s_out = (ctypes.c_void_p(st.cuda_stream) for st in streams)
-  n_buf = 3
-  ev_buf = [torch.empty(shape[0], dtype=torch.float32, device=device) for _ in range(n_buf)]
-  y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
-  y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-  name = 'event_cbcsr_matvec_heter_float_float'
-  opaque = event_ops._cb_descriptor(shape[0], shape[1], cb.block_width, cb.scale_log2, cb.team_lanes_log2)
-  ws = [torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device) for _ in range(n_buf)]
-  target = _lib.target(name)
-  bufs = [(ctypes.c_void_p * 5)(cb.groups.data_ptr(), cb.offsets.data_ptr(), ev_buf[b].data_ptr(), y_buf[b].data_ptr(),
-                                ws[b].data_ptr()) for b in range(n_buf)]
-
-  def new_event():
-    e = ctypes.c_void_p()
-    check(rt.cudaEventCreateWithFlags(ctypes.byref(e), 2))   # cudaEventDisableTiming
-    return e
-  done_in, done_c, done_out = ([new_event() for _ in range(n_buf)] for _ in range(3))
-  used = [False] * n_buf
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  h2d, d2h = 4 * shape[0], 4 * shape[1]
-
-  def run(first, count, timed):
-    torch.cuda.synchronize()
-    for b in range(n_buf):
-      used[b] = False
-    if timed:
-      e0.record(streams[0])
-    for i in range(count):
-      s, b = first + i, i % n_buf
-      if used[b]:
-        check(rt.cudaStreamWaitEvent(s_in, done_c[b], 0))      # the spike buffer's previous reader has finished
-        check(rt.cudaStreamWaitEvent(s_c, done_out[b], 0))     # the result buffer's previous copy-out has finished
-      if 'in' in parts:
-        check(rt.cudaMemcpyAsync(ev_buf[b].data_ptr(), ev_host[s].data_ptr(), h2d, 1, s_in))
-      check(rt.cudaEventRecord(done_in[b], s_in))
-      check(rt.cudaStreamWaitEvent(s_c, done_in[b], 0))
-      if 'compute' in parts:
-        target(s_c, bufs[b], opaque, len(opaque))
-      check(rt.cudaEventRecord(done_c[b], s_c))
-      check(rt.cudaStreamWaitEvent(s_out, done_c[b], 0))
-      if 'out' in parts:
-        check(rt.cudaMemcpyAsync(y_host[b].data_ptr(), y_buf[b].data_ptr(), d2h, 2, s_out))
-      check(rt.cudaEventRecord(done_out[b], s_out))
-      used[b] = True
-    _lib.check_status()
-    if timed:
-      streams[2].wait_stream(streams[1])
-      streams[2].wait_stream(streams[0])
-      e1.record(streams[2])
-    torch.cuda.synchronize()
-
-  run(0, max(W, 1), False)
-  run(W, K, True)
-  if len(parts) < 3:      # a partial run (diagnosis): only the time means anything
-    return {'ms': e0.elapsed_time(e1), 'h2d': h2d, 'd2h': d2h}
-  last = (K - 1) % n_buf
-  if not torch.isfinite(y_host[last]).all() or float(y_host[last].abs().sum()) == 0.0:
+def run_e2e_single(torch, work, ev_host, shape, W, K, device, cb):
+  """End to end with HOST buffers through the library's public call for it (brainpylib_b200.HostSteps ->
+  bpl_run_host_steps -> the custom-call target on the prepared matrix): every step copies that step's spike vector
+  from pinned host memory to the device, runs the target and copies the result back to pinned host memory.  Three
+  streams (copy in, compute, copy out) over rings of three buffers, enqueued by native code; time = CUDA events
+  around the whole run."""
+  import brainpylib_b200 as bpl
+  from brainpylib_b200 import event_ops
+  runner = bpl.HostSteps(cb, shape=shape, events_dtype=torch.float32)
+  y_host = torch.empty((3, shape[1]), dtype=torch.float32).pin_memory()
+  runner.run(ev_host[:max(W, 1)], y_host)
+  y_host.fill_(0.0)
+  ms = runner.run(ev_host[W:W + K], y_host)
+  last = y_host[(K - 1) % 3]
+  if not torch.isfinite(last).all() or float(last.abs().sum()) == 0.0:
     raise SystemExit('e2e: the result copied back to the host is empty')
   want = event_ops.event_cbcsr_matvec_raw(cb, ev_host[W + K - 1].to(device))
-  if not torch.allclose(y_host[last].to(device), want, rtol=1e-5, atol=1e-2):
+  if not torch.allclose(last.to(device), want, rtol=1e-5, atol=1e-2):
     raise SystemExit('e2e: the result copied back to the host differs from the operator result')
-  return {'ms': e0.elapsed_time(e1), 'h2d': h2d, 'd2h': d2h}
+  return {'ms': ms, 'h2d': 4 * shape[0], 'd2h': 4 * shape[1]}
 
 
 def run_sharded(args, torch, dist, device, world):
-  """N > 1: plain CSR shards by post-synaptic range, one launch per step (push of the next step's spike list to
-  every peer fused with this step's scatter)."""
+  """N > 1: shards by post-synaptic range, one launch per step (push of the next step's spike list to every peer
+  fused with this step's scatter).  Headline: the shard prepared into the column-blocked layout (float accumulation);
+  the same step on the plain CSR shard is timed beside it."""
   from brainpylib_b200 import _lib, event_ops, gpu_ops, sharded
   rank = dist.get_rank()
   K, W = args.steps, args.warmup
@@ -659,26 +618,41 @@ def run_sharded(args, torch, dist, device, world):
   exchange = sharded.PushExchange(n_neurons, dtype=torch.float32, device=device, slots=4)
   n_y = 3
   y_ring = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_y)]
+  t0 = time.perf_counter()
+  prepared = event_ops.csr_to_column_blocked(work['data'], work['indices'], work['indptr'], shape=shape,
+                                             block_width=event_ops.default_block_width(shape[1], device, reserve=4))
+  torch.cuda.synchronize()
+  prepare_ms = (time.perf_counter() - t0) * 1e3
 
-  def run_steps(first, count):
+  def run_steps(first, count, layout):
     exchange.prime(ev_dev_mine[first], y_ring[0])
     for i in range(count):
       last = i == count - 1
-      exchange.step(work['data'], work['indices'], work['indptr'], y_ring[i % n_y],
-                    None if last else y_ring[(i + 1) % n_y], None if last else ev_dev_mine[first + i + 1])
+      y_next, ev_next = (None, None) if last else (y_ring[(i + 1) % n_y], ev_dev_mine[first + i + 1])
+      if layout == 'prepared':
+        exchange.step_prepared(prepared, y_ring[i % n_y], y_next, ev_next)
+      else:
+        exchange.step(work['data'], work['indices'], work['indptr'], y_ring[i % n_y], y_next, ev_next)
 
   sampler = ClockSampler(device.index)
   side = torch.cuda.Stream(device)
-  with sampler:
+  graphs = []
+  want = event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], ev_dev_full, shape=shape,
+                                        transpose=True)
+
+  def timed_run(layout):
+    """K steps captured in one graph, CUDA events on every rank between barriers, maximum over ranks; the last
+    step checked against the stand-alone operator on the assembled spike vector."""
     with torch.cuda.stream(side):
-      run_steps(0, min(max(W, 3), W + K))
+      run_steps(0, min(max(W, 3), W + K), layout)
     torch.cuda.synchronize()
     dist.barrier()
     graph, warm = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=side):
-      run_steps(W, K)
+      run_steps(W, K, layout)
     with torch.cuda.graph(warm, stream=side):
-      run_steps(0, max(W, 1))
+      run_steps(0, max(W, 1), layout)
+    graphs.extend((graph, warm))
     warm.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -691,29 +665,37 @@ def run_sharded(args, torch, dist, device, world):
     dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
     exchange.check_all(dist)
-    # the last step against the stand-alone operator on the assembled spike vector
     y_last = y_ring[(K - 1) % n_y].clone()
-    want = event_ops.event_csr_matvec_raw(work['data'], work['indices'], work['indptr'], ev_dev_full, shape=shape,
-                                          transpose=True)
     torch.cuda.synchronize()
     if not torch.allclose(y_last, want, rtol=1e-5, atol=1e-2):
-      raise SystemExit('sharded step: the result of the last step differs from the stand-alone operator')
+      raise SystemExit(f'sharded step ({layout}): the result of the last step differs from the stand-alone operator')
+    return t.item()
+
+  with sampler:
+    ms_csr = timed_run('csr')
+    ms = timed_run('prepared')
     # the scatter of this rank's shard alone (stand-alone operator on the assembled vector), for the roofline
     name = 'event_csr_matvec_heter_float_float'
     opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
     ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
     ev_rot = [torch.from_numpy(ev_all[W + i]).to(device) for i in range(min(K, 8))]
     y_tmp = torch.empty(shape[1], dtype=torch.float32, device=device)
-    k_ms = kernel_time_ms(torch, lib, lambda s: event_ops.event_csr_matvec_raw(
+    k_ms_csr = kernel_time_ms(torch, lib, lambda s: event_ops.event_csr_matvec_raw(
       work['data'], work['indices'], work['indptr'], ev_rot[s % len(ev_rot)], shape=shape, transpose=True, out=y_tmp,
       workspace=ws), 0, min(K, 16))
+    cb_name = 'event_cbcsr_matvec_heter_float_float'
+    cb_opaque = event_ops._cb_descriptor(shape[0], shape[1], prepared.block_width, prepared.scale_log2,
+                                         prepared.team_lanes_log2)
+    cb_ws = torch.empty(_lib.workspace_bytes(cb_name, cb_opaque), dtype=torch.uint8, device=device)
+    k_ms = kernel_time_ms(torch, lib, lambda s: event_ops.event_cbcsr_matvec_raw(
+      prepared, ev_rot[s % len(ev_rot)], out=y_tmp, workspace=cb_ws), 0, min(K, 16))
     # ---- e2e: own spikes in, own slice of the result out, every step, through the exchange ----
-    e2e = run_e2e_sharded(torch, dist, work, exchange, ev_host_mine, shape, W, K, device, want)
+    e2e = run_e2e_sharded(torch, dist, prepared, exchange, ev_host_mine, shape, W, K, device, want)
   n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
   s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
-  k_bytes = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
+  k_bytes = 6.0 * s_local + 8.0 * n_act * prepared.n_blocks + 4.0 * shape[1]
+  k_bytes_csr = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
   step_bytes = k_bytes + 4.0 * per + 4.0 * shape[1] + 4.0 * n_act * world
   achieved = k_bytes / (k_ms * 1e-3) / 1e9
   line = {
@@ -722,25 +704,32 @@ def run_sharded(args, torch, dist, device, world):
     'data': 'synthetic',
     'config': {'workload': WORKLOAD if n_neurons == N_NEURONS else f'REDUCED TWIN of C3: {n_neurons} neurons x 1000 synapses',
                'l2': 'inputs larger than L2 in total: each step streams a different part of the 8 GB matrix',
-               'sharding': f'post-synaptic neurons (matrix columns) split over {world} ranks, plain CSR shards; each rank '
-                           'owns 1/N of the spike sources; ONE launch per step: the kernel pushes the compacted spikes of '
-                           'step s+1 into every peer over NVLink (peer stores), waits (bounded) for the lists of step s and '
-                           'scatters them; no collective on the data path'},
+               'sharding': f'post-synaptic neurons (matrix columns) split over {world} ranks, each shard prepared once into '
+                           'the column-blocked layout; each rank owns 1/N of the spike sources; ONE launch per step: the '
+                           'kernel pushes the compacted spikes of step s+1 into every peer over NVLink (peer stores), waits '
+                           '(bounded) for the lists of step s and scatters them; no collective on the data path'},
     'e2e': {'value': total_ops / (e2e['ms'] * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'],
             'd2h_bytes_per_step': e2e['d2h'], 'ms_per_step': e2e['ms'] / K,
-            'path': 'PushExchange.prime / step (bpl_sharded_prime / bpl_sharded_step): per rank its own n/N spikes from '
-                    'pinned host memory in, its own slice of the result out to pinned host memory, every step'},
+            'path': 'PushExchange.run_host_steps (bpl_sharded_run_host_steps: bpl_sharded_prime, then bpl_sharded_cb_step per '
+                    'step): per rank its own n/N spikes from pinned host memory in, its own slice of the result out to '
+                    'pinned host memory, every step'},
     'gpu_launches': K + 1,     # prime once, then one kernel per step
-    'roofline': {'bound': 'hbm', 'kernel': 'row_scatter_kernel<float, heter, list, vec> on one rank\'s shard (stand-alone)',
+    'roofline': {'bound': 'hbm', 'kernel': 'event_cb_scatter_kernel on one rank\'s prepared shard (stand-alone)',
                  'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
-                 'traffic': 1.046 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
+                 'traffic': 1.14 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
                  'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
                  'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
                           'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak}},
+    'prepared_matrix': {'bytes': prepared.nbytes(), 'block_width': prepared.block_width, 'n_blocks': prepared.n_blocks,
+                        'team_lanes': 1 << prepared.team_lanes_log2, 'prepare_ms': prepare_ms},
+    'plain_csr_shards': {'value': total_ops / (ms_csr * 1e-3), 'unit': UNIT, 'ms_per_step': ms_csr / K,
+                         'path': 'PushExchange.step (bpl_sharded_step) on the plain CSR shard, same graph-of-K-steps timing',
+                         'kernel_us': k_ms_csr * 1e3,
+                         'roofline_frac': k_bytes_csr / (k_ms_csr * 1e-3) / 1e9 / peak},
     'clocks': sampler.summary(),
   }
   if rank == 0:
-    print(json.dumps(line), flush=True)
+    emit(line)
   # Tear down in a fixed order: the captured graphs must go before the communicator.  A process that still
   # cannot finish the teardown within 30 s leaves anyway: the measurement is complete and printed.
   sys.stdout.flush()
@@ -750,107 +739,37 @@ def run_sharded(args, torch, dist, device, world):
   watchdog.start()
   torch.cuda.synchronize()
   dist.barrier()
-  graph.reset()
-  warm.reset()
+  for g in graphs:
+    g.reset()
   torch.cuda.synchronize()
   dist.destroy_process_group()
   watchdog.cancel()
 
 
-def run_e2e_sharded(torch, dist, work, exchange, ev_host_mine, shape, W, K, device, want_last):
-  """End to end on N ranks: per step a rank copies ITS OWN n/N spikes of the next step from pinned host memory,
-  runs the one-launch step (push to the peers + scatter of the current step) and copies ITS OWN slice of the
-  result to pinned host memory.  Copy-in, compute and copy-out run on three streams with three spike buffers and
-  three result buffers; the CUDA runtime and the library are driven directly, step by step.  Time: CUDA events
-  on every rank between two barriers, maximum over ranks."""
-  import ctypes
-  from brainpylib_b200 import _lib
-  rt = ctypes.CDLL('libcudart.so.12')
-  rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
-  rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint]
-  rt.cudaEventRecord.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
-  rt.cudaStreamWaitEvent.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+def run_e2e_sharded(torch, dist, prepared, exchange, ev_host_mine, shape, W, K, device, want_last):
+  """End to end on N ranks through PushExchange.run_host_steps (bpl_sharded_run_host_steps): per step a rank copies
+  ITS OWN n/N spikes of the next step from pinned host memory, runs the one-launch step (push to the peers + scatter
+  of the current step) and copies ITS OWN slice of the result to pinned host memory, on three streams over rings of
+  three buffers.  Time: CUDA events around the run on every rank, started together after a barrier, maximum over
+  ranks."""
+  y_host = torch.empty((3, shape[1]), dtype=torch.float32).pin_memory()
 
-  def check(code):
-    if code != 0:
-      raise SystemExit(f'CUDA runtime call failed with error {code}')
-
-  streams = [torch.cuda.Stream(device) for _ in range(3)]
-  s_in, s_c, s_out = (ctypes.c_void_p(st.cuda_stream) for st in streams)
-  n_buf = 3
-  per = ev_host_mine.shape[1]
-  ev_buf = [torch.empty(per, dtype=torch.float32, device=device) for _ in range(n_buf)]
-  y_buf = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(n_buf)]
-  y_host = [torch.empty(shape[1], dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-  h2d, d2h = 4 * per, 4 * shape[1]
-
-  def new_event():
-    e = ctypes.c_void_p()
-    check(rt.cudaEventCreateWithFlags(ctypes.byref(e), 2))   # cudaEventDisableTiming
-    return e
-  # done_in[b]: spikes copied into ev_buf[b]; pushed[b]: the launch that pushed ev_buf[b] has finished;
-  # done_c[b]: the launch that scattered into y_buf[b] has finished; done_out[b]: y_buf[b] has reached the host
-  done_in, pushed, done_c, done_out = ([new_event() for _ in range(n_buf)] for _ in range(4))
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-
-  # everything a step needs is marshalled once: no Python work between the launches beyond the calls themselves
-  ev_ptr = [t.data_ptr() for t in ev_buf]
-  y_ptr = [t.data_ptr() for t in y_buf]
-  yh_ptr = [t.data_ptr() for t in y_host]
-  host_base = ev_host_mine.data_ptr()
-  mid_step = [exchange.step_call(work['data'], work['indices'], work['indptr'], y_buf[b], y_buf[(b + 1) % n_buf],
-                                 ev_buf[(b + 1) % n_buf], s_c) for b in range(n_buf)]
-  last_step = [exchange.step_call(work['data'], work['indices'], work['indptr'], y_buf[b], None, None, s_c)
-               for b in range(n_buf)]
-
-  def copy_in(first, j):            # spikes of step first + j into ev_buf[j % n_buf]
-    b = j % n_buf
-    if j >= n_buf:
-      check(rt.cudaStreamWaitEvent(s_in, pushed[b], 0))
-    check(rt.cudaMemcpyAsync(ev_ptr[b], host_base + (first + j) * h2d, h2d, 1, s_in))
-    check(rt.cudaEventRecord(done_in[b], s_in))
-
-  def run(first, count, timed):
+  def run(first, count):
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    if timed:
-      e0.record(streams[0])
-    copy_in(first, 0)
-    check(rt.cudaStreamWaitEvent(s_c, done_in[0], 0))
-    exchange.prime(ev_buf[0], y_buf[0], stream=s_c)
-    check(rt.cudaEventRecord(pushed[0], s_c))
-    for i in range(count):
-      last = i == count - 1
-      b, nb = i % n_buf, (i + 1) % n_buf
-      if not last:
-        copy_in(first, i + 1)
-        check(rt.cudaStreamWaitEvent(s_c, done_in[nb], 0))
-        if i + 1 >= n_buf:
-          check(rt.cudaStreamWaitEvent(s_c, done_out[nb], 0))   # y_buf[nb] is zero-filled by this launch
-      (last_step if last else mid_step)[b]()
-      if not last:
-        check(rt.cudaEventRecord(pushed[nb], s_c))
-      check(rt.cudaEventRecord(done_c[b], s_c))
-      check(rt.cudaStreamWaitEvent(s_out, done_c[b], 0))
-      check(rt.cudaMemcpyAsync(yh_ptr[b], y_ptr[b], d2h, 2, s_out))
-      check(rt.cudaEventRecord(done_out[b], s_out))
-    _lib.check_status()
-    if timed:
-      streams[2].wait_stream(streams[1])
-      e1.record(streams[2])
+    ms = exchange.run_host_steps(prepared, ev_host_mine[first:first + count], y_host)
     torch.cuda.synchronize()
     dist.barrier()
+    return ms
 
-  run(0, max(W, 1), False)
-  run(W, K, True)
-  t = torch.tensor([e0.elapsed_time(e1)], device=device)
+  run(0, max(W, 1))
+  t = torch.tensor([run(W, K)], device=device)
   dist.all_reduce(t, op=dist.ReduceOp.MAX)
   exchange.check_all(dist)
-  last = (K - 1) % n_buf
-  if not torch.allclose(y_host[last].to(device), want_last, rtol=1e-5, atol=1e-2):
+  if not torch.allclose(y_host[(K - 1) % 3].to(device), want_last, rtol=1e-5, atol=1e-2):
     raise SystemExit('e2e: the slice copied back to the host differs from the stand-alone operator result')
-  return {'ms': t.item(), 'h2d': h2d, 'd2h': d2h}
+  return {'ms': t.item(), 'h2d': 4 * ev_host_mine.shape[1], 'd2h': 4 * shape[1]}
 
 
 def main():
@@ -866,10 +785,12 @@ def main():
   ap.add_argument('--neurons', type=int, default=N_NEURONS,
                   help='reduced twin of the workload (multiple of 100000), for profiler captures only')
   args = ap.parse_args()
+  keep_stdout_for_the_result()
   if args.warmup < 3 and args.impl == 'ours':
     log('[bench] note: fewer than 3 warm-up steps requested; the timing rules ask for >= 3')
   if args.config != 'c3':
     import bench_configs
+    bench_configs.RESULT_OUT = _RESULT_OUT
     return bench_configs.main([args.config, '--warmup', str(args.warmup)])
   if args.impl == 'reference':
     run_reference(args)

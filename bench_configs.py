@@ -123,9 +123,14 @@ def ref_cuda_entry(us, what, ours_us):
           'timing': 'CUDA events around the reference wrapper on the legacy default stream, best of 3'}
 
 
+RESULT_OUT = None        # bench.py sets this to the stream that takes the JSON lines (default: stdout)
+
+
 def emit(**kw):
   if int(os.environ.get('RANK', '0')) == 0:     # replicas (every configuration but c5) report once
-    print(json.dumps(kw), flush=True)
+    out = RESULT_OUT if RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(kw) + '\n')
+    out.flush()
 
 
 def bench_c1(args, device):

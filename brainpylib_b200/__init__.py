@@ -19,3 +19,5 @@ from . import compat
 from .compat import *
 from . import neuron_ops
 from .neuron_ops import *
+from . import host_steps
+from .host_steps import HostSteps

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libbrainpylib_b200.so')
 BUILD_DIR = os.path.join(HERE, 'csrc', 'build')
 SOURCES = ['csr_kernels.cu', 'cbcsr_kernels.cu', 'cbcsr_build.cu', 'jitconn_kernels.cu', 'jitconn_matmat_versions.cu', 'jitconn_event_v1.cu', 'neuron_kernels.cu', 'scatter_kernels.cu', 'event_info_kernels.cu',
-           'exchange_kernels.cu', 'gpu_ops.cc']
+           'exchange_kernels.cu', 'host_steps.cc', 'gpu_ops.cc']
 HEADERS = ['abi.h', 'common.cuh', 'spike_scan.cuh', 'row_scatter.cuh', 'cb_scatter.cuh', os.path.join('..', '..', 'include', 'brainpylib_b200.h')]
 NVCC = os.environ.get('NVCC', 'nvcc')
 FLAGS = ['-O3', '-std=c++17', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo',

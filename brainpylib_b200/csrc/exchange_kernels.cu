@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "spike_scan.cuh"
 #include "row_scatter.cuh"
+#include "cb_scatter.cuh"
 
 namespace bpl {
 namespace {
@@ -79,14 +80,24 @@ struct ListTable {
 
 // Block-wide: compacts chunk `chunk_in_rank` (<= 4096 events) of this rank's events and stores the ids and
 // the count into every peer's list (`lists[p] + list_offset`) at chunk index `chunk_index`.  Ends with the
-// block's stores issued but not fenced.  `warp_total`: shared, SCAN_THREADS / 32 words.
+// block's stores issued but not fenced.  `warp_total`: shared, SCAN_THREADS / 32 words.  `stage`: shared, 16-byte
+// aligned, SCAN_TILE words: the ids are compacted there first and leave as 16-byte stores, a few per peer
+// instead of one 4-byte peer store per spike (an SM keeps only so many peer stores in flight).
+// `tid`: index of the thread in its team of 256 (the whole block for 256-thread blocks); `bar`: 0 = the block
+// barrier, else the id of a named barrier that the 256 threads of the team share (1024-thread blocks run four teams).
+__device__ __forceinline__ void team_sync(const int bar) {
+    if (bar == 0) __syncthreads();
+    else asm volatile("bar.sync %0, 256;" :: "r"(bar) : "memory");
+}
+
 template<typename E>
 __device__ __forceinline__ void compact_and_push_chunk(const E *__restrict__ events, const uint32_t n_local,
                                                        const uint32_t row_offset, uint32_t *const *lists,
                                                        const size_t list_offset, const int world,
                                                        const uint32_t chunk_in_rank, const uint32_t chunk_index,
-                                                       uint32_t *warp_total) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+                                                       uint32_t *warp_total, uint32_t *stage,
+                                                       const uint32_t tid = threadIdx.x, const int bar = 0) {
+    const uint32_t lane = tid & 31, warp = tid >> 5;
     const uint32_t begin = chunk_in_rank * SCAN_TILE;
     const uint32_t end = min(begin + static_cast<uint32_t>(SCAN_TILE), n_local);
     const uint32_t base = begin + warp * SCAN_WARP_SPAN;
@@ -102,9 +113,9 @@ __device__ __forceinline__ void compact_and_push_chunk(const E *__restrict__ eve
         bits[k] = __ballot_sync(FULL_MASK, act[k]);
         total += __popc(bits[k]);
     }
-    __syncthreads();               // warp_total may still be read from an earlier use
+    team_sync(bar);                // warp_total may still be read from an earlier use
     if (lane == 0) warp_total[warp] = total;
-    __syncthreads();
+    team_sync(bar);
     uint32_t offset = 0, chunk_total = 0;
 #pragma unroll
     for (int w = 0; w < SCAN_THREADS / 32; ++w) {
@@ -116,14 +127,19 @@ __device__ __forceinline__ void compact_and_push_chunk(const E *__restrict__ eve
     const size_t seg = list_offset + static_cast<size_t>(MAX_CHUNKS) + static_cast<size_t>(chunk_index) * SCAN_TILE;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-        if (act[k]) {
-            const uint32_t at = offset + __popc(bits[k] & below);
-            const uint32_t row = row_offset + base + k * 32 + lane;
-            for (int p = 0; p < world; ++p) lists[p][seg + at] = row;
-        }
+        if (act[k]) stage[offset + __popc(bits[k] & below)] = row_offset + base + k * 32 + lane;
         offset += __popc(bits[k]);
     }
-    if (threadIdx.x < static_cast<uint32_t>(world)) lists[threadIdx.x][list_offset + chunk_index] = chunk_total;
+    team_sync(bar);
+    // whole 16-byte words: up to three entries behind the count are written too (they stay inside the chunk's
+    // segment and nobody reads behind the count)
+    const uint32_t n4 = (chunk_total + 3u) >> 2;
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage);
+    for (int p = 0; p < world; ++p) {
+        uint4 *dst = reinterpret_cast<uint4 *>(lists[p] + seg);
+        for (uint32_t i = tid; i < n4; i += SCAN_THREADS) dst[i] = src[i];
+    }
+    if (tid < static_cast<uint32_t>(world)) lists[tid][list_offset + chunk_index] = chunk_total;
 }
 
 // Block-wide, after the block's peer stores: the block reports in on `counter`; the last of `n_blocks`
@@ -173,8 +189,9 @@ spike_scan_push_kernel(const E *__restrict__ events, const uint32_t n_local, con
                        const ListTable peers, const int world, const int rank, const int slot,
                        const uint32_t chunks_per_rank, uint32_t *__restrict__ cta_counter) {
     __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    __shared__ __align__(16) uint32_t stage[SCAN_TILE];
     compact_and_push_chunk(events, n_local, row_offset, peers.list, 0, world, blockIdx.x,
-                           rank * chunks_per_rank + blockIdx.x, warp_total);
+                           rank * chunks_per_rank + blockIdx.x, warp_total, stage);
     publish_arrival(cta_counter + MAX_WORLD, gridDim.x, peers.flags, world, rank, slot);   // counter 16
 }
 
@@ -206,7 +223,7 @@ __device__ __noinline__ void step_exchange(float *__restrict__ y_next, const uin
                                            const ListTable &peers, const size_t slot_words, uint32_t *state,
                                            const int world, const int rank, const int slots,
                                            const uint32_t max_polls, const uint32_t pushers, bool *arrived,
-                                           uint32_t *warp_total) {
+                                           uint32_t *warp_total, uint32_t *stage) {
     uint32_t *ctr = state + slots + 1;
     const uint32_t t = ctr[CTR_STEP_T];
     const int slot = static_cast<int>(t % slots), next_slot = static_cast<int>((t + 1u) % slots);
@@ -218,7 +235,7 @@ __device__ __noinline__ void step_exchange(float *__restrict__ y_next, const uin
         for (uint32_t c = blockIdx.x; c < chunks_per_rank; c += pushers)
             compact_and_push_chunk(next_events, n_local, row_offset, peers.list,
                                    static_cast<size_t>(next_slot) * slot_words, world, c,
-                                   rank * chunks_per_rank + c, warp_total);
+                                   rank * chunks_per_rank + c, warp_total, stage);
         publish_arrival(ctr + CTR_STEP_PUSH, pushers, peers.flags, world, rank, next_slot);
         if (threadIdx.x == 0) *arrived = false;
     } else if (threadIdx.x < 32) {
@@ -241,12 +258,13 @@ sharded_step_kernel(const uint32_t *__restrict__ indices, const uint32_t *__rest
                     const int world, const int rank, const int slots, const uint32_t max_polls) {
     __shared__ uint32_t prefix[MAX_CHUNKS + 1];
     __shared__ uint32_t warp_total[ROW_WARPS];
+    __shared__ __align__(16) uint32_t stage[SCAN_TILE];
     __shared__ bool arrived;
     // few enough pushing blocks that the scatter keeps (nearly) the whole grid, each taking several chunks in
     // turn: their work is short next to the scatter and off its critical path
     const uint32_t pushers = next_events == nullptr ? 0u : min(chunks_per_rank, max(gridDim.x / 16u, 1u));
     step_exchange(y_next, n_out, next_events, n_local, row_offset, chunks_per_rank, peers, slot_words, state, world,
-                  rank, slots, max_polls, pushers, &arrived, warp_total);
+                  rank, slots, max_polls, pushers, &arrived, warp_total, stage);
     if (arrived) {
         const uint32_t slot = state[slots + 1 + CTR_STEP_T] % slots;
         const uint32_t *list = peers.list[rank] + static_cast<size_t>(slot) * slot_words;
@@ -267,6 +285,90 @@ sharded_step_kernel(const uint32_t *__restrict__ indices, const uint32_t *__rest
     }
 }
 
+// The same step on a shard stored in the column-blocked layout (cb_scatter.cuh): blocks [0, n_scatter) are the
+// (column block, row share) CTAs of the scatter, with the block's slice of the output in shared memory; the blocks
+// behind them exchange, four 256-thread teams per block, each compacting and pushing one chunk at a time.
+template<int NBUF, bool FIXED, int LOG_L>
+__global__ void __launch_bounds__(CB_THREADS, 1)
+sharded_cb_step_kernel(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets, const uint32_t n_out,
+                       const uint32_t width, const uint32_t n_blocks, const uint32_t P, float *__restrict__ y_cur,
+                       float *__restrict__ y_next, const void *__restrict__ next_events, const int ev_is_float,
+                       const uint32_t n_local, const uint32_t row_offset, const uint32_t chunks_per_rank,
+                       const __grid_constant__ ListTable peers, const size_t slot_words, uint32_t *state, const int world,
+                       const int rank, const int slots, const uint32_t max_polls, const uint32_t acc_bytes,
+                       const float inv_scale) {
+    extern __shared__ __align__(128) unsigned char cb_smem[];
+    __shared__ uint32_t prefix[MAX_CHUNKS + 1];
+    __shared__ uint32_t warp_total[CB_WARPS];
+    __shared__ bool arrived;
+    uint32_t *ctr = state + slots + 1;
+    const uint32_t n_scatter = n_blocks * P;
+    const uint32_t t = ctr[CTR_STEP_T];
+    const int slot = static_cast<int>(t % slots), next_slot = static_cast<int>((t + 1u) % slots);
+    if (y_next != nullptr)
+        for (uint32_t i = blockIdx.x * CB_THREADS + threadIdx.x; i < n_out; i += gridDim.x * CB_THREADS) y_next[i] = 0.0f;
+    if (blockIdx.x >= n_scatter) {
+        // ---- exchange: the rank's spikes of step t + 1 go to slot (t + 1) % slots of every peer ----
+        const uint32_t team = threadIdx.x >> 8, tid = threadIdx.x & 255u;
+        const uint32_t n_teams = (gridDim.x - n_scatter) * 4u;
+        for (uint32_t c = (blockIdx.x - n_scatter) * 4u + team; c < chunks_per_rank; c += n_teams) {
+            if (ev_is_float)
+                compact_and_push_chunk(static_cast<const float *>(next_events), n_local, row_offset, peers.list,
+                                       static_cast<size_t>(next_slot) * slot_words, world, c, rank * chunks_per_rank + c,
+                                       warp_total + team * 8u, reinterpret_cast<uint32_t *>(cb_smem) + team * SCAN_TILE,
+                                       tid, 1 + static_cast<int>(team));
+            else
+                compact_and_push_chunk(static_cast<const uint8_t *>(next_events), n_local, row_offset, peers.list,
+                                       static_cast<size_t>(next_slot) * slot_words, world, c, rank * chunks_per_rank + c,
+                                       warp_total + team * 8u, reinterpret_cast<uint32_t *>(cb_smem) + team * SCAN_TILE,
+                                       tid, 1 + static_cast<int>(team));
+        }
+        publish_arrival(ctr + CTR_STEP_PUSH, gridDim.x - n_scatter, peers.flags, world, rank, next_slot);
+    } else {
+        // ---- scatter of step t from the lists every rank pushed during its previous launch ----
+        if (threadIdx.x < 32) {
+            const bool ok = poll_arrivals(peers.flags[rank], world, slot, t / slots + 1u, max_polls);
+            if (threadIdx.x == 0) {
+                arrived = ok;
+                if (!ok) state[slots] = 1u;    // timed out: the output of this step must not be trusted
+            }
+        }
+        __syncthreads();
+        if (arrived) {
+            const uint32_t *list = peers.list[rank] + static_cast<size_t>(slot) * slot_words;
+            cb_scatter_body<NBUF, FIXED, LOG_L>(groups, offsets, n_out, width, n_blocks, blockIdx.x / P, blockIdx.x % P, P,
+                                                SCAN_TILE, chunks_per_rank * world, list, list + MAX_CHUNKS, y_cur,
+                                                acc_bytes, cb_smem, prefix, warp_total, inv_scale);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(ctr + CTR_STEP_EXIT, 1u);
+        if (done == gridDim.x - 1) {           // every block has read t and finished
+            ctr[CTR_STEP_EXIT] = 0u;
+            state[t % slots] = t / slots + 1u;
+            ctr[CTR_STEP_T] = t + 1u;
+        }
+    }
+}
+
+using CbStepKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, float *, float *,
+                              const void *, int, uint32_t, uint32_t, uint32_t, const ListTable, size_t, uint32_t *, int, int,
+                              int, uint32_t, uint32_t, float);
+template<int NBUF, bool FIXED>
+CbStepKernel cb_step_for_lanes(uint32_t log_l) {
+    switch (log_l) {
+        case 3: return sharded_cb_step_kernel<NBUF, FIXED, 3>;
+        case 4: return sharded_cb_step_kernel<NBUF, FIXED, 4>;
+        case 5: return sharded_cb_step_kernel<NBUF, FIXED, 5>;
+        default: return sharded_cb_step_kernel<NBUF, FIXED, 2>;
+    }
+}
+CbStepKernel cb_step_kernel(uint32_t n_buf, bool fixed, uint32_t log_l) {
+    if (n_buf == 3) return fixed ? cb_step_for_lanes<3, true>(log_l) : cb_step_for_lanes<3, false>(log_l);
+    return fixed ? cb_step_for_lanes<2, true>(log_l) : cb_step_for_lanes<2, false>(log_l);
+}
+
 // Pushes the spikes of the step the counter points at (the first step of a run) and zero-fills its output.
 template<typename E>
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -275,12 +377,13 @@ sharded_prime_kernel(const E *__restrict__ events, const uint32_t n_local, const
                      uint32_t *state, const int world, const int rank, const int slots,
                      float *__restrict__ y_first, const uint32_t n_out) {
     __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    __shared__ __align__(16) uint32_t stage[SCAN_TILE];
     uint32_t *ctr = state + slots + 1;
     const int slot = static_cast<int>(ctr[CTR_STEP_T] % slots);
     for (uint32_t i = blockIdx.x * SCAN_THREADS + threadIdx.x; i < n_out; i += gridDim.x * SCAN_THREADS)
         y_first[i] = 0.0f;
     compact_and_push_chunk(events, n_local, row_offset, peers.list, static_cast<size_t>(slot) * slot_words, world,
-                           blockIdx.x, rank * chunks_per_rank + blockIdx.x, warp_total);
+                           blockIdx.x, rank * chunks_per_rank + blockIdx.x, warp_total, stage);
     publish_arrival(ctr + CTR_STEP_PUSH, gridDim.x, peers.flags, world, rank, slot);
 }
 
@@ -470,6 +573,65 @@ void bpl_sharded_step(bpl_stream_t stream, const void *data, const void *indices
     if (ev_is_float) { if (vec) BPL_STEP_LAUNCH(float, true); else BPL_STEP_LAUNCH(float, false); }
     else             { if (vec) BPL_STEP_LAUNCH(uint8_t, true); else BPL_STEP_LAUNCH(uint8_t, false); }
 #undef BPL_STEP_LAUNCH
+    launch_ok();
+}
+
+// The same step on a shard prepared into the column-blocked layout (bpl_cbcsr_plan / bpl_cbcsr_fill with the rank's
+// column range): groups / offsets / block_width / fixed_point / scale_log2 / team_lanes_log2 as for
+// event_cbcsr_matvec_*; n_out = columns of the shard.  y_cur must already be zero.
+void bpl_sharded_cb_step(bpl_stream_t stream, const void *groups, const void *offsets, uint32_t n_out, uint32_t block_width,
+                         int fixed_point, int scale_log2, uint32_t team_lanes_log2, void *y_cur, void *y_next,
+                         const void *next_events, int ev_is_float, uint32_t n_local, uint32_t row_offset,
+                         void *const *peer_lists, size_t slot_bytes, void *const *peer_flags, void *state, int world,
+                         int rank, int slots, uint32_t max_polls) {
+    if (!step_arguments_ok(n_local, world, rank, slots, state)) return;
+    if (groups == nullptr || offsets == nullptr || y_cur == nullptr || peer_lists == nullptr || peer_flags == nullptr ||
+        slot_bytes % 16 != 0 || !aligned16(groups) || n_out == 0) {
+        set_status(BPL_ERR_ARGUMENT, "sharded step: null or misaligned matrix, output or peer table, or a slot size that is "
+                                     "not a multiple of 16 bytes");
+        return;
+    }
+    if (block_width == 0 || block_width > CB_MAX_WIDTH || (block_width & 31u) != 0 ||
+        (team_lanes_log2 != 0 && (team_lanes_log2 < 2 || team_lanes_log2 > 5)) ||
+        (fixed_point && (scale_log2 < -100 || scale_log2 > 100))) {
+        set_status(BPL_ERR_ARGUMENT, "sharded step: bad block_width, team_lanes_log2 or scale_log2");
+        return;
+    }
+    const uint32_t n_blocks = (n_out + block_width - 1) / block_width;
+    const CbPlan plan = cb_plan(block_width);
+    if (n_blocks > CB_MAX_BLOCKS || !plan.ok) {
+        set_status(BPL_ERR_ARGUMENT, "sharded step: too many column blocks, or no shared memory left for the copy buffers");
+        return;
+    }
+    const uint32_t cpr = bpl_spike_list_chunks_per_rank(n_local);
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    // exchange blocks: four chunks at a time each, at most four blocks; the rest of the SMs scatter
+    uint32_t pushers = next_events == nullptr ? 0u : (cpr + 3u) / 4u;
+    pushers = pushers > 4u ? 4u : pushers;
+    uint32_t P = (sms > pushers ? sms - pushers : 1u) / n_blocks;
+    P = P < 1 ? 1u : (P > 32 ? 32u : P);
+    const uint32_t log_l = team_lanes_log2 == 0 ? 2u : team_lanes_log2;
+    const CbStepKernel kernel = cb_step_kernel(plan.n_buf, fixed_point != 0, log_l);
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        for (uint32_t nb = 2; nb <= 3; ++nb)
+            for (int fx = 0; fx < 2; ++fx)
+                for (uint32_t ll = 2; ll <= 5; ++ll)
+                    if (cudaFuncSetAttribute(cb_step_kernel(nb, fx != 0, ll), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(CB_SMEM_LIMIT)) != cudaSuccess) {
+                        launch_ok();
+                        return;
+                    }
+        configured_device = dev;
+    }
+    const ListTable t = list_table(peer_lists, peer_flags, world);
+    const float inv_scale = fixed_point ? ldexpf(1.0f, -scale_log2) : 1.0f;
+    kernel<<<n_blocks * P + pushers, CB_THREADS, plan.smem_bytes, stream>>>(
+        static_cast<const unsigned char *>(groups), static_cast<const uint32_t *>(offsets), n_out, block_width, n_blocks, P,
+        static_cast<float *>(y_cur), static_cast<float *>(y_next), next_events, ev_is_float, n_local, row_offset, cpr, t,
+        slot_bytes / 4, static_cast<uint32_t *>(state), world, rank, slots, max_polls, plan.acc_bytes, inv_scale);
     launch_ok();
 }
 

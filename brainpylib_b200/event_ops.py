@@ -295,15 +295,22 @@ class ColumnBlockedCSR:
     return sum(t.numel() * t.element_size() for t in (self.groups, self.offsets))
 
 
-def default_block_width(n_col, device=None):
-  """Columns per block: as many blocks as give every SM one CTA when each block is shared by 4 CTAs,
-  at least 1024 columns, at most what leaves room for three copy buffers per warp beside the block's
-  slice of the output in a CTA's shared memory; a multiple of 32."""
+def default_block_width(n_col, device=None, reserve=0):
+  """Columns per block.  The kernel gives every column block ``P = floor(SMs / n_blocks)`` CTAs, one per SM, so the
+  choice is the number of blocks: at least ``n_col / 20480`` (a block's slice of the output and three copy buffers
+  per warp must fit a CTA's shared memory; wide blocks mean long row segments, which stream best), and more only
+  where that fills at least 10 % more of the SMs.  ``reserve``: SMs to leave free (the one-launch sharded step runs
+  up to four exchanging blocks beside the scatter).  At least 1024 columns, a multiple of 32."""
   sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
-  n_blocks = max(1, sms // 4)
-  width = -(-n_col // n_blocks)
-  width = min(max(width, 1024), 20480)
-  return -(-width // 32) * 32
+  sms = max(1, sms - reserve)
+  least = max(1, -(-n_col // 20480))
+  best, best_ctas = least, least * max(1, sms // least)
+  for n_blocks in range(least + 1, min(2 * least, sms) + 1):
+    ctas = n_blocks * (sms // n_blocks)
+    if ctas * 100 >= best_ctas * 110:
+      best, best_ctas = n_blocks, ctas
+  width = max(-(-n_col // best), 1024)
+  return min(-(-width // 32) * 32, 20480)
 
 
 def check_block_width(block_width):
@@ -324,9 +331,11 @@ def csr_to_column_blocked(data, indices, indptr, *, shape, block_width=None, col
   times faster than floats.  One more pass finds ``M``, the largest sum of ``|w|`` over any column, and the
   unit is ``2^-k`` with ``k = floor(log2(2^30 / M))``: no spike pattern can overflow.  Every weight is
   rounded to a multiple of the unit, so an output fed by ``n`` active synapses is off by at most
-  ``n * 2^-(k+1)``, about ``n * M * 2^-31``, and carries no other rounding (integer sums are exact and
-  order-independent).  With weights of similar magnitude that is the accuracy of float32 summation; a
-  column that mixes huge and tiny weights keeps the tiny ones only to that absolute step."""
+  ``n * 2^-(k+1)``, about ``n * M * 2^-31``; the integer sum inside a CTA is exact and order-independent, and
+  the only float32 roundings left are the conversion of each CTA's sum and the addition of the few CTAs that
+  share a column block (so two launches that split the rows differently may differ in the last bit).  With
+  weights of similar magnitude that is the accuracy of float32 summation; a column that mixes huge and tiny
+  weights keeps the tiny ones only to that absolute step."""
   import ctypes
   n_row, n_col = int(shape[0]), int(shape[1])
   lo, hi = (0, n_col) if col_range is None else (int(col_range[0]), int(col_range[1]))

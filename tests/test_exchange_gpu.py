@@ -119,3 +119,58 @@ def test_fused_step_times_out_without_a_prime(cuda):
   with pytest.raises(Exception):
     ex.check()
   assert float(y.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize('dtype,shape,density,accumulate,width',
+                         [(torch.float32, (9000, 3000), 0.01, 'float', 1024), (torch.bool, (9000, 3000), 0.01, 'fixed', 512),
+                          # 49 chunks of events over 16 exchanging teams: each pushes several chunks in turn
+                          (torch.float32, (200000, 3000), 0.002, 'float', None),
+                          (torch.bool, (70000, 40000), 0.003, 'fixed', 20416)])
+def test_fused_step_on_a_prepared_shard_matches_the_operator(cuda, dtype, shape, density, accumulate, width):
+  """world = 1: the one-launch step on the column-blocked layout (exchange blocks beside the scatter's (block, share)
+  CTAs) gives, step after step and across slot reuse, what the stand-alone prepared operator gives: within float32
+  summation order, and with fixed-point accumulation within the rounding of adding the few CTA shares of a block
+  (the two launches split the rows over a different number of CTAs)."""
+  import cases
+  import brainpylib_b200 as bpl
+  data, indices, indptr, rng = cases.csr_case(shape, density, 29)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=shape, block_width=width, accumulate=accumulate)
+  ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=1000)
+  steps = 6
+  evs = []
+  for s in range(steps):
+    ev = torch.as_tensor(rng.random(shape[0]) < (0.3 if s % 2 else 0.01)).to(cuda)
+    evs.append(ev if dtype == torch.bool else ev.float() * 2.0)
+  y = [torch.full((shape[1],), float('nan'), device=cuda) for _ in range(2)]
+  ex.prime(evs[0], y[0])
+  launches = [ex.step_prepared_call(prepared, y[s % 2], y[(s + 1) % 2] if s + 1 < steps else None,
+                                    evs[s + 1] if s + 1 < steps else None, torch.cuda.current_stream().cuda_stream)
+              for s in range(steps)]
+  for s in range(steps):
+    if s % 2:
+      launches[s]()
+    else:
+      ex.step_prepared(prepared, y[s % 2], y[(s + 1) % 2] if s + 1 < steps else None, evs[s + 1] if s + 1 < steps else None)
+    want = bpl.event_csr_matvec(d, ix, ptr, evs[s], shape=shape, transpose=True, prepared=prepared)
+    if accumulate == 'fixed':
+      torch.testing.assert_close(y[s % 2], want, rtol=1e-6, atol=1e-5)
+    else:
+      torch.testing.assert_close(y[s % 2], want, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(want, bpl.event_csr_matvec(d, ix, ptr, evs[s], shape=shape, transpose=True),
+                               rtol=1e-4, atol=1e-3)
+  ex.check()
+
+
+def test_prepared_step_refuses_a_shard_of_another_shape(cuda):
+  import cases
+  import brainpylib_b200 as bpl
+  data, indices, indptr, _ = cases.csr_case((3000, 2000), 0.01, 3)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=(3000, 2000), block_width=1024)
+  ex = sharded.PushExchange(4000, dtype=torch.float32, device=cuda, slots=4, max_polls=50)
+  with pytest.raises(ValueError, match='rows'):
+    ex.step_prepared(prepared, torch.zeros(2000, device=cuda), None, None)
+  ex = sharded.PushExchange(3000, dtype=torch.float32, device=cuda, slots=4, max_polls=50)
+  with pytest.raises(ValueError, match='entries of the shard'):
+    ex.step_prepared(prepared, torch.zeros(1999, device=cuda), None, None)

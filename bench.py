@@ -78,7 +78,7 @@ def measured_peaks():
       return float(json.load(open(path))['hbm_gbs']), 'measured (MEASURED_PEAKS.json hbm_gbs)'
     except Exception:
       pass
-  return 6650.0, 'fallback (6.65 TB/s, earlier measurement on this pool)'
+  return 6650.0, 'fallback (6.65 TB/s: MEASURED_PEAKS.json is absent)'
 
 
 # ------------------------------------------------------------------------------------------------

@@ -56,6 +56,8 @@ static_assert(sizeof(MatMatJITProbDescriptor1) == 40 && offsetof(MatMatJITProbDe
 
 // Status of the last target call on this host thread (defined in gpu_ops.cc).
 void set_status(int code, const char *message);
+// bytes of the connection lists of the *_v1_ws matmat targets (jitconn_kernels.cu); elem = sizeof(T)
+size_t matmat_list_workspace_bytes(const char *opaque, size_t opaque_len, size_t elem);
 
 // The reference's UnpackDescriptor throws std::runtime_error("Invalid opaque object size")
 // (lib/kernel_helpers.h:34-40); here the mismatch is recorded and the call returns.

@@ -109,6 +109,11 @@ size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t o
         if (opaque == nullptr || opaque_len != 24) return 0;
         return bpl_event_csr_workspace_bytes(*reinterpret_cast<const uint32_t *>(opaque), 1);
     }
+    if (std::strncmp(target_name, "gpu_matmat_prob_prob_", 21) == 0) {
+        const size_t len = std::strlen(target_name);
+        if (len < 6 || std::strcmp(target_name + len - 6, "_v1_ws") != 0) return 0;
+        return bpl::matmat_list_workspace_bytes(opaque, opaque_len, std::strstr(target_name, "_double_") ? 8 : 4);
+    }
     if (std::strncmp(target_name, "nonzero_", 8) == 0) {
         if (opaque == nullptr || opaque_len != sizeof(DoubleSizeDescriptor)) return 0;
         return bpl_nonzero_workspace_bytes(reinterpret_cast<const DoubleSizeDescriptor *>(opaque)->size_y);

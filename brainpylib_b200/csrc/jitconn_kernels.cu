@@ -339,18 +339,53 @@ template<typename T> struct MMTile;
 template<> struct MMTile<float> { static constexpr int KT = 512; static constexpr int CHUNKS = 8; };    // 64 KB
 template<> struct MMTile<double> { static constexpr int KT = 256; static constexpr int CHUNKS = 16; };  // 64 KB
 
+// Stages X[m_i .. m_i+31][k0 .. k0+KT) transposed into `tile` ([KT][MM_ROWS]): lane = row of X, so the 32 stores of
+// a warp go to 32 consecutive words (no bank conflict); each lane reads VEC consecutive k from its own row (the
+// other half of a touched sector is picked up from L1 by the next iteration).  Rows and columns past the matrix read
+// as zero.
+template<typename T, int KT>
+__device__ __forceinline__ void mm_stage_tile(T *tile, const T *__restrict__ X, const unsigned int m_i,
+                                              const unsigned int m, const unsigned int k, const unsigned int k0,
+                                              const bool vec_ok, const unsigned int lane, const unsigned int warp) {
+    constexpr int VEC = 16 / sizeof(T);
+    const unsigned int r = lane;
+    const bool row_ok = m_i + r < m;
+    const T *src = X + static_cast<size_t>(m_i + r) * k + k0;
+    for (unsigned int kk = warp * VEC; kk < KT; kk += (MM_THREADS / 32) * VEC) {
+        T v[VEC];
+        if (vec_ok && row_ok && k0 + kk + VEC <= k) {
+            const uint4 u = *reinterpret_cast<const uint4 *>(src + kk);
+            *reinterpret_cast<uint4 *>(v) = u;
+        } else {
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) v[q] = (row_ok && k0 + kk + q < k) ? src[kk + q] : T(0);
+        }
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) tile[(kk + q) * MM_ROWS + r] = v[q];
+    }
+}
+
 template<typename T, int KIND>
 __global__ void __launch_bounds__(MM_THREADS, 2)
 jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double log_p, const double w1,
                   const double w2, const unsigned int m, const unsigned int k, const unsigned int n,
-                  T *__restrict__ Y) {
+                  T *__restrict__ Y, const unsigned int col0 = 0, const unsigned int *__restrict__ cnt = nullptr,
+                  const unsigned int cap = 0, const unsigned int *__restrict__ n_over = nullptr) {
     constexpr int KT = MMTile<T>::KT, CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS]
 
-    const unsigned long long n_i64 = static_cast<unsigned long long>(blockIdx.x) * MM_THREADS + threadIdx.x;
-    const bool live = n_i64 < n;
+    // columns col0 + blockIdx.x * MM_THREADS + threadIdx.x, below n.  With `cnt`: only the columns whose connection
+    // list did not fit its `cap` slots (the list-driven kernel leaves those to this one); normally there are none
+    // and every block returns at once.
+    const unsigned long long n_i64 = col0 + static_cast<unsigned long long>(blockIdx.x) * MM_THREADS + threadIdx.x;
+    bool live = n_i64 < n;
     const unsigned int n_i = static_cast<unsigned int>(n_i64);
+    if (cnt != nullptr) {
+        if (*n_over == 0u) return;
+        live = live && cnt[n_i - col0] > cap;
+        if (!__syncthreads_or(live)) return;
+    }
     const unsigned int m_i = blockIdx.y * MM_ROWS;
     const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const bool vec_ok = (k % (16 / sizeof(T)) == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
@@ -363,27 +398,7 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
     for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
 
     for (unsigned int k0 = 0; k0 < k; k0 += KT) {
-        // stage X[m_i .. m_i+31][k0 .. k0+KT) transposed: lane = row of X, so the 32 stores of a warp go
-        // to 32 consecutive words (no bank conflict); each lane reads VEC consecutive k from its own row
-        // (the other half of a touched sector is picked up from L1 by the next iteration)
-        {
-            constexpr int VEC = 16 / sizeof(T);
-            const unsigned int r = lane;
-            const bool row_ok = m_i + r < m;
-            const T *src = X + static_cast<size_t>(m_i + r) * k + k0;
-            for (unsigned int kk = warp * VEC; kk < KT; kk += (MM_THREADS / 32) * VEC) {
-                T v[VEC];
-                if (vec_ok && row_ok && k0 + kk + VEC <= k) {
-                    const uint4 u = *reinterpret_cast<const uint4 *>(src + kk);
-                    *reinterpret_cast<uint4 *>(v) = u;
-                } else {
-#pragma unroll
-                    for (int q = 0; q < VEC; ++q) v[q] = (row_ok && k0 + kk + q < k) ? src[kk + q] : T(0);
-                }
-#pragma unroll
-                for (int q = 0; q < VEC; ++q) tile[(kk + q) * MM_ROWS + r] = v[q];
-            }
-        }
+        mm_stage_tile<T, KT>(tile, X, m_i, m, k, k0, vec_ok, lane, warp);
         __syncthreads();
         const unsigned int k_end = min(k0 + KT, k);
         while (pos < k_end) {
@@ -419,6 +434,128 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
             for (int i = 0; i < PER_CHUNK; ++i) {
                 const unsigned int row = m_i + chunk * PER_CHUNK + i;
                 if (row < m) Y[static_cast<size_t>(row) * n + n_i] = sum[c * PER_CHUNK + i];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Y = X @ M with every column's stream generated ONCE (targets *_v1_ws: one more buffer, a workspace)
+// ------------------------------------------------------------------------------------------
+// jit_matmat_kernel regenerates the stream of a column for every group of 32 rows of X (8 times for 256 rows), as
+// the reference does, and that generator work is most of its time.  Here one pass walks every column's stream once
+// and writes its connections, position and weight (the same draws, the same conversions), into a workspace; a second
+// pass is the multiply alone: the same thread = (column, 32 rows) mapping, the same transposed K-tiles of X in shared
+// memory, the same order of additions (same bits), with (position, weight) read from the list.
+//
+// Workspace of one chunk of C columns (C a multiple of MM_THREADS; the host walks the columns chunk by chunk):
+//   n_over u32 (+ padding to 256 B) | cnt u32[C] | pos u32[(C / 32) * cap * 32] | w T[(C / 32) * cap * 32]
+// Entry j of column c sits at ((c / 32) * cap + j) * 32 + c % 32: the 32 columns of a warp are interleaved, so a
+// warp that stores (or loads) entry j of all its columns touches one 128-byte line per array.
+// cap = expected connections per column + 10 standard deviations + 16.  A column with more (never seen; the bound
+// is not a proof) is counted in n_over and recomputed whole by jit_matmat_kernel in its overflow-only mode, so the
+// result is exact whatever the draws.
+template<typename T, int KIND>
+__global__ void __launch_bounds__(256)
+jit_matmat_fill_kernel(const unsigned int seed, const double log_p, const double w1, const double w2,
+                       const unsigned int k, const unsigned int n, const unsigned int col0, const unsigned int cap,
+                       unsigned int *__restrict__ cnt, unsigned int *__restrict__ pos_list, T *__restrict__ w_list,
+                       unsigned int *__restrict__ n_over) {
+    const unsigned int c = blockIdx.x * 256u + threadIdx.x;     // column within the chunk
+    const unsigned long long n_i64 = static_cast<unsigned long long>(col0) + c;
+    if (n_i64 >= n) return;
+    Stream s(seed + static_cast<unsigned int>(n_i64), log_p);
+    curandState &st = s.st;
+    const size_t base = static_cast<size_t>(c >> 5) * cap * 32u + (c & 31u);
+    unsigned int count = 0;
+    unsigned int pos = s.ugap();
+    while (pos < k) {
+        T rand;
+        if (KIND == W_NORMAL) rand = (T) (curand_normal(&st) * w2 + w1);
+        else rand = (T) (curand_uniform(&st) * w2 + w1);
+        if (count < cap) {
+            pos_list[base + static_cast<size_t>(count) * 32u] = pos;
+            w_list[base + static_cast<size_t>(count) * 32u] = rand;
+        }
+        ++count;
+        pos += s.ugap();
+    }
+    cnt[c] = count;
+    if (count > cap) atomicAdd(n_over, 1u);
+}
+
+template<typename T> struct MMListTile;
+template<> struct MMListTile<float> { static constexpr int KT = 768; };    // 96 KB, two blocks per SM
+template<> struct MMListTile<double> { static constexpr int KT = 384; };
+
+template<typename T>
+__global__ void __launch_bounds__(MM_THREADS, (sizeof(T) == 8 ? 1 : 2))     // 32 double sums need more than 64 registers
+jit_matmat_apply_kernel(const T *__restrict__ X, const unsigned int m, const unsigned int k, const unsigned int n,
+                        const unsigned int col0, const unsigned int cap, const unsigned int *__restrict__ cnt,
+                        const unsigned int *__restrict__ pos_list, const T *__restrict__ w_list, T *__restrict__ Y) {
+    constexpr int KT = MMListTile<T>::KT, CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS]
+
+    const unsigned int c = blockIdx.x * MM_THREADS + threadIdx.x;
+    const unsigned long long n_i64 = static_cast<unsigned long long>(col0) + c;
+    const bool live = n_i64 < n;
+    const unsigned int n_i = static_cast<unsigned int>(n_i64);
+    const unsigned int m_i = blockIdx.y * MM_ROWS;
+    const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool vec_ok = (k % (16 / sizeof(T)) == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
+
+    const unsigned int stored = live ? cnt[c] : 0u;
+    const bool fits = stored <= cap;                 // else: the overflow pass writes this column
+    const unsigned int count = fits ? stored : 0u;
+    const size_t base = static_cast<size_t>(c >> 5) * cap * 32u + lane;
+    unsigned int j = 0;
+    unsigned int pos = count > 0 ? pos_list[base] : 0xffffffffu;
+    T rand = count > 0 ? w_list[base] : T(0);
+    T sum[MM_ROWS];
+#pragma unroll
+    for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
+
+    for (unsigned int k0 = 0; k0 < k; k0 += KT) {
+        mm_stage_tile<T, KT>(tile, X, m_i, m, k, k0, vec_ok, lane, warp);
+        __syncthreads();
+        const unsigned int k_end = min(k0 + KT, k);
+        while (pos < k_end) {
+            // the next entry is requested before this one is applied
+            const unsigned int jn = j + 1;
+            const bool more = jn < count;
+            const unsigned int pos_n = more ? pos_list[base + static_cast<size_t>(jn) * 32u] : 0xffffffffu;
+            const T rand_n = more ? w_list[base + static_cast<size_t>(jn) * 32u] : T(0);
+            const T *row = tile + (pos - k0) * MM_ROWS;
+#pragma unroll
+            for (int cc = 0; cc < CHUNKS; ++cc) {
+                const unsigned int chunk = (cc + lane) & (CHUNKS - 1);
+                if (sizeof(T) == 4) {
+                    const float4 x = *reinterpret_cast<const float4 *>(row + chunk * PER_CHUNK);
+                    sum[cc * 4 + 0] += (x.x * rand);
+                    sum[cc * 4 + 1] += (x.y * rand);
+                    sum[cc * 4 + 2] += (x.z * rand);
+                    sum[cc * 4 + 3] += (x.w * rand);
+                } else {
+                    const double2 x = *reinterpret_cast<const double2 *>(row + chunk * PER_CHUNK);
+                    sum[cc * 2 + 0] += (x.x * rand);
+                    sum[cc * 2 + 1] += (x.y * rand);
+                }
+            }
+            j = jn;
+            pos = pos_n;
+            rand = rand_n;
+        }
+        __syncthreads();
+    }
+    if (live && fits) {
+#pragma unroll
+        for (int cc = 0; cc < CHUNKS; ++cc) {
+            const unsigned int chunk = (cc + lane) & (CHUNKS - 1);
+#pragma unroll
+            for (int i = 0; i < PER_CHUNK; ++i) {
+                const unsigned int row = m_i + chunk * PER_CHUNK + i;
+                if (row < m) Y[static_cast<size_t>(row) * n + n_i] = sum[cc * PER_CHUNK + i];
             }
         }
     }
@@ -564,7 +701,105 @@ void jit_matmat_impl(cudaStream_t stream, void **buffers, const char *opaque, si
     launch_ok();
 }
 
+// ---- list-driven matmat: capacity, chunking, workspace ----
+constexpr size_t MM_LIST_BUDGET = 768ull << 20;     // bytes of lists one chunk of columns may take
+// tests: force a small capacity (the overflow pass runs) or a small budget (several chunks of columns)
+unsigned int g_mm_list_cap_override = 0;
+size_t g_mm_list_budget_override = 0;
+
+struct MMListPlan {
+    unsigned int cap;        // list slots per column
+    unsigned int chunk;      // columns per chunk (multiple of MM_THREADS)
+    size_t cnt_off, pos_off, w_off, bytes;
+};
+
+inline MMListPlan mm_list_plan(unsigned int k, unsigned int n, double log_p, size_t elem) {
+    MMListPlan p;
+    const double prob = -expm1(log_p);                        // log_p = log(1 - conn_prob)
+    const double mean = static_cast<double>(k) * prob;
+    const double cap_d = ceil(mean + 10.0 * sqrt(mean * (1.0 - prob) + 1.0)) + 16.0;
+    p.cap = static_cast<unsigned int>(cap_d < static_cast<double>(k) + 16.0 ? cap_d : static_cast<double>(k) + 16.0);
+    if (g_mm_list_cap_override != 0) p.cap = g_mm_list_cap_override;
+    const size_t per_col = static_cast<size_t>(p.cap) * (4 + elem) + 4;
+    const size_t n_round = (static_cast<size_t>(n) + MM_THREADS - 1) / MM_THREADS * MM_THREADS;
+    const size_t budget = g_mm_list_budget_override != 0 ? g_mm_list_budget_override : MM_LIST_BUDGET;
+    size_t chunk = budget / per_col / MM_THREADS * MM_THREADS;
+    if (chunk < static_cast<size_t>(MM_THREADS)) chunk = MM_THREADS;
+    if (chunk > n_round) chunk = n_round;
+    p.chunk = static_cast<unsigned int>(chunk);
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    p.cnt_off = 256;
+    p.pos_off = up(p.cnt_off + 4 * chunk);
+    p.w_off = up(p.pos_off + 4 * chunk * p.cap);
+    p.bytes = up(p.w_off + elem * chunk * p.cap);
+    return p;
+}
+
+template<typename T, int KIND>
+void jit_matmat_list_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    const MatMatJITProbDescriptor1 *d = unpack<MatMatJITProbDescriptor1>(opaque, opaque_len);
+    if (!d) return;
+    const T *X = static_cast<const T *>(buffers[0]);
+    T *Y = static_cast<T *>(buffers[1]);
+    unsigned char *ws = static_cast<unsigned char *>(buffers[2]);
+    if (d->m == 0 || d->n == 0) return;
+    const unsigned int gy = blocks_for(d->m, MM_ROWS);
+    if (gy > 65535u) {
+        set_status(BPL_ERR_ARGUMENT, "matmat: more than 65535 * 32 rows in the dense operand");
+        return;
+    }
+    if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) {
+        set_status(BPL_ERR_ARGUMENT, "matmat: the workspace is missing or not aligned to 256 bytes");
+        return;
+    }
+    const MMListPlan p = mm_list_plan(d->k, d->n, d->log_p, sizeof(T));
+    constexpr size_t smem_apply = static_cast<size_t>(MMListTile<T>::KT) * MM_ROWS * sizeof(T);
+    constexpr size_t smem_inline = static_cast<size_t>(MMTile<T>::KT) * MM_ROWS * sizeof(T);
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        if (cudaFuncSetAttribute(jit_matmat_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem_apply)) != cudaSuccess ||
+            cudaFuncSetAttribute(jit_matmat_kernel<T, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem_inline)) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        configured_device = dev;
+    }
+    unsigned int *n_over = reinterpret_cast<unsigned int *>(ws);
+    unsigned int *cnt = reinterpret_cast<unsigned int *>(ws + p.cnt_off);
+    unsigned int *pos_list = reinterpret_cast<unsigned int *>(ws + p.pos_off);
+    T *w_list = reinterpret_cast<T *>(ws + p.w_off);
+    for (unsigned long long col0 = 0; col0 < d->n; col0 += p.chunk) {
+        const unsigned int cols = static_cast<unsigned int>(
+            d->n - col0 < p.chunk ? d->n - col0 : static_cast<unsigned long long>(p.chunk));
+        const unsigned int c0 = static_cast<unsigned int>(col0);
+        if (cudaMemsetAsync(n_over, 0, sizeof(unsigned int), stream) != cudaSuccess) {
+            launch_ok();
+            return;
+        }
+        jit_matmat_fill_kernel<T, KIND><<<blocks_for(cols, 256), 256, 0, stream>>>(
+            d->seed, d->log_p, d->w1, d->w2, d->k, d->n, c0, p.cap, cnt, pos_list, w_list, n_over);
+        const dim3 grid(blocks_for(cols, MM_THREADS), gy);
+        jit_matmat_apply_kernel<T><<<grid, MM_THREADS, smem_apply, stream>>>(
+            X, d->m, d->k, d->n, c0, p.cap, cnt, pos_list, w_list, Y);
+        jit_matmat_kernel<T, KIND><<<grid, MM_THREADS, smem_inline, stream>>>(
+            X, d->seed, d->log_p, d->w1, d->w2, d->m, d->k, d->n, Y, c0, cnt, p.cap, n_over);
+    }
+    launch_ok();
+}
+
 }  // namespace
+
+size_t matmat_list_workspace_bytes(const char *opaque, size_t opaque_len, size_t elem) {
+    if (opaque == nullptr || opaque_len != sizeof(MatMatJITProbDescriptor1)) return 0;
+    const MatMatJITProbDescriptor1 *d = reinterpret_cast<const MatMatJITProbDescriptor1 *>(opaque);
+    if (d->n == 0) return 256;
+    return mm_list_plan(d->k, d->n, d->log_p, elem).bytes;
+}
+
 }  // namespace bpl
 
 using namespace bpl;
@@ -612,5 +847,19 @@ JIT_MATMAT(gpu_matmat_prob_prob_normal_float_v1, float, W_NORMAL)
 JIT_MATMAT(gpu_matmat_prob_prob_normal_double_v1, double, W_NORMAL)
 JIT_MATMAT(gpu_matmat_prob_prob_uniform_float_v1, float, W_UNIFORM)
 JIT_MATMAT(gpu_matmat_prob_prob_uniform_double_v1, double, W_UNIFORM)
+#define JIT_MATMAT_LIST(name, T, KIND) \
+    void name(bpl_stream_t s, void **b, const char *o, size_t n) { jit_matmat_list_impl<T, KIND>(s, b, o, n); }
+JIT_MATMAT_LIST(gpu_matmat_prob_prob_normal_float_v1_ws, float, W_NORMAL)
+JIT_MATMAT_LIST(gpu_matmat_prob_prob_normal_double_v1_ws, double, W_NORMAL)
+JIT_MATMAT_LIST(gpu_matmat_prob_prob_uniform_float_v1_ws, float, W_UNIFORM)
+JIT_MATMAT_LIST(gpu_matmat_prob_prob_uniform_double_v1_ws, double, W_UNIFORM)
+
+// Tests only: non-zero values replace the computed list capacity per column and the byte budget of one chunk of
+// columns (0 restores them), so that a small matrix overflows its lists (the recomputation pass runs) or is walked
+// in several chunks.
+void bpl_matmat_list_limits_for_tests(uint32_t cap, size_t budget_bytes) {
+    g_mm_list_cap_override = cap;
+    g_mm_list_budget_override = budget_bytes;
+}
 
 }  // extern "C"

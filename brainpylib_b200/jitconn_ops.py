@@ -83,16 +83,38 @@ def event_matvec_raw(events, *, kind, w1=0., w2=0., conn_prob, shape, seed, tran
   return out
 
 
-def matmat_raw(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None, version='v1'):
+def matmat_raw(matrix, *, kind, w1, w2, conn_prob, shape, seed, out=None, version='v1', workspace=True):
   """Primitive ``matmat_prob_{uniform,normal}``: ``Y = X @ M``; target ``gpu_matmat_prob_prob_<kind>_<T>_<version>``
-  as brainpylib/_src/jitconn_ops/matmat.py:443-466 builds it."""
+  as brainpylib/_src/jitconn_ops/matmat.py:443-466 builds it.  ``version='v1'`` runs the ``_v1_ws`` target (same
+  bits, every column's stream generated once, lists in a workspace) unless ``workspace=False`` or a tensor to use
+  as the workspace is passed."""
   m, k = matrix.shape
   opaque = gpu_ops.build_matmat_jit_prob_descriptor1(m, k, shape[1], seed, _log_p(conn_prob), w1, w2)
   name = 'gpu_matmat_prob_prob_' + kind + float_suffix(matrix.dtype) + '_' + version
   if out is None:
     out = torch.empty((m, shape[1]), dtype=matrix.dtype, device=matrix.device)
-  _lib.call(name, [matrix, out], opaque, device=matrix.device)
+  if version == 'v1' and workspace is not False:
+    name += '_ws'
+    if workspace is True:
+      workspace = _matmat_workspace(matrix.device, _lib.workspace_bytes(name, opaque))
+    _lib.call(name, [matrix, out, workspace], opaque, device=matrix.device)
+  else:
+    _lib.call(name, [matrix, out], opaque, device=matrix.device)
   return out
+
+
+_MATMAT_WS = {}
+
+
+def _matmat_workspace(device, nbytes):
+  """One scratch buffer per device, grown on demand (calls on one device are stream-ordered)."""
+  ws = _MATMAT_WS.get(device)
+  if ws is None or ws.numel() < nbytes:
+    ws = None
+    _MATMAT_WS.pop(device, None)
+    ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    _MATMAT_WS[device] = ws
+  return ws
 
 
 class _Matvec(torch.autograd.Function):

@@ -84,6 +84,10 @@ size_t bpl_build_cbcsr_descriptor(uint32_t n_row, uint32_t n_col, uint32_t block
  * more (discarded) uint8 output, the way the reference's `event_info` returns a second
  * array (brainpylib/_src/event_ops/event_info_collection.py:115-122). */
 size_t bpl_workspace_bytes(const char *target_name, const char *opaque, size_t opaque_len);
+/* Tests only: non-zero values replace the per-column list capacity and the byte budget of one chunk of columns of
+ * the *_v1_ws matmat targets (0 restores the computed ones), so that a small matrix overflows its lists (the
+ * recomputation pass runs) or is walked in several chunks. */
+void bpl_matmat_list_limits_for_tests(uint32_t cap, size_t budget_bytes);
 
 /* ---- profiling hook (no counterpart in the reference) -------------------------------------
  * When both are non-NULL cudaEvent_t handles, every later event_csr_matvec_* call with
@@ -162,6 +166,10 @@ void bpl_profile_scatter_events(void *before, void *after);
  * gpu_matmat_prob_prob_{normal,uniform}_{float,double}_v1
  *   replaces lib/gpu_jitconn_matmat.cu:279-317,364-402 (lib/gpu_ops.cc:171-174)
  *   opaque  MatMatJITProbDescriptor1{m,k,n,seed,log_p,w1,w2}; buffers [X T(m,k), Y T(m,n)] row-major
+ * gpu_matmat_prob_prob_{normal,uniform}_{float,double}_v1_ws      (no counterpart in the reference)
+ *   The same product, bit for bit, with every column's stream generated once instead of once per 32 rows of X:
+ *   one pass writes the connections (position, weight) of a chunk of columns into the workspace, a second multiplies
+ *   from the lists.  buffers [X T(m,k), Y T(m,n), workspace (bpl_workspace_bytes(), 256-byte aligned)]; same opaque.
  * gpu_matmat_prob_prob_normal_{float,double}_{v2,v3}
  *   replace lib/gpu_jitconn_matmat.cu:138-231 (v2: 32 streams per column, one per range of ceil(k / 32) rows) and
  *   :19-135 (v3: one stream per row of X, pairs shared by a block of rows); registered lib/gpu_ops.cc:166-169.
@@ -234,6 +242,10 @@ void bpl_profile_scatter_events(void *before, void *after);
     X(gpu_matmat_prob_prob_normal_double_v3)                        \
     X(gpu_matmat_prob_prob_uniform_float_v1)                        \
     X(gpu_matmat_prob_prob_uniform_double_v1)                       \
+    X(gpu_matmat_prob_prob_normal_float_v1_ws)                      \
+    X(gpu_matmat_prob_prob_normal_double_v1_ws)                     \
+    X(gpu_matmat_prob_prob_uniform_float_v1_ws)                     \
+    X(gpu_matmat_prob_prob_uniform_double_v1_ws)                    \
     X(nonzero_bool) X(nonzero_int) X(nonzero_long) X(nonzero_float) X(nonzero_double) \
     BPL_FOR_EACH_FI(X, gpu_csr_event_sum_homo)                      \
     BPL_FOR_EACH_FI(X, gpu_csr_event_sum_heter)                     \

@@ -422,3 +422,31 @@ def test_counter_based_event_matvec_refuses_what_it_has_no_kernel_for(cuda):
     bpl.event_matvec_prob_conn_homo_weight(ev, 1.0, conn_prob=0.1, shape=(5, 10), seed=1, version='v1', outdim_parallel=False)
   with pytest.raises(ValueError):
     bpl.event_matvec_prob_conn_homo_weight(ev, 1.0, conn_prob=0.1, shape=(5, 10), seed=1, version='v3')
+
+
+@pytest.mark.parametrize('kind,w1,w2', KINDS[1:])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float64])
+def test_matmat_from_lists_is_bit_identical_to_the_inline_kernel(cuda, kind, w1, w2, dtype):
+  """The *_v1_ws targets (streams generated once into lists, then multiplied) against the *_v1 targets (the
+  reference's structure: stream regenerated per 32 rows) over ragged sizes; then with a list capacity of 3 slots,
+  where most columns overflow and are recomputed by the inline kernel; then with a byte budget that walks the
+  columns in several chunks; then both."""
+  import ctypes
+  from brainpylib_b200 import _lib
+  lib = _lib.lib()
+  lib.bpl_matmat_list_limits_for_tests.argtypes = [ctypes.c_uint32, ctypes.c_size_t]
+  lib.bpl_matmat_list_limits_for_tests.restype = None
+  g = torch.Generator(device='cpu').manual_seed(17)
+  sizes = [(5, (100, 200), 0.1), (33, (1000, 10), 0.2), (64, (777, 1301), 0.03), (40, (3000, 2500), 0.01),
+           (1, (64, 513), 1.0)]
+  try:
+    for cap, budget in ((0, 0), (3, 0), (0, 40000), (7, 40000)):
+      lib.bpl_matmat_list_limits_for_tests(cap, budget)
+      for m, shape, prob in sizes:
+        X = torch.randn(m, shape[0], generator=g, dtype=dtype).to(cuda)
+        kw = dict(kind=kind, w1=w1, w2=w2, conn_prob=prob, shape=shape, seed=2 ** 32 - 100)   # the seed wraps
+        plain = jitconn_ops.matmat_raw(X, workspace=False, **kw)
+        listed = jitconn_ops.matmat_raw(X, **kw)
+        assert torch.equal(plain, listed), (cap, budget, m, shape, prob)
+  finally:
+    lib.bpl_matmat_list_limits_for_tests(0, 0)

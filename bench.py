@@ -341,10 +341,50 @@ def run_ours(args):
   _lib.lib()   # fail loudly if the CUDA library is missing
   if args.neurons % workloads_chunk_rows() != 0 or args.neurons % world != 0:
     raise SystemExit('--neurons must be a multiple of 100000 and of the number of ranks')
-  if world == 1:
+  if world == 1 and args.one_rank_of > 1:
+    run_one_rank_of(args, torch, device)
+  elif world == 1:
     run_single(args, torch, device)
   else:
     run_sharded(args, torch, dist, device, world)
+
+
+def run_one_rank_of(args, torch, device):
+  """Profiler aid, not a benchmark result: ONE process stands in for rank 0 of `--one-rank-of N` ranks.  It holds
+  that rank's shard of the matrix (columns 0 .. n/N, prepared) and runs the one-launch sharded step on an exchange
+  of world size 1.  Every step is primed separately (the prime call pushes all n spike sources, which N ranks would
+  share) and the step launch itself pushes nothing, so the launch that is timed and captured is the scatter half of
+  a rank's step: bounded poll, scatter of the assembled list on the 1/N shard, exit ticket.  Prints one JSON line
+  marked as a profiler aid."""
+  from brainpylib_b200 import event_ops, sharded
+  K, W = args.steps, args.warmup
+  n = args.neurons
+  work = build_workload(W + K, keep_host_matrix=False, device=device, shard=(0, args.one_rank_of), n_neurons=n)
+  shape = work['shape']
+  prepared = event_ops.csr_to_column_blocked(work['data'], work['indices'], work['indptr'], shape=shape,
+                                             block_width=event_ops.default_block_width(shape[1], device, reserve=4))
+  ev = [torch.from_numpy(e).to(device) for e in work['events']]
+  exchange = sharded.PushExchange(n, dtype=torch.float32, device=device, slots=4)
+  y = [torch.empty(shape[1], dtype=torch.float32, device=device) for _ in range(2)]
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+  def run(first, count):
+    total = 0.0
+    for i in range(count):
+      exchange.prime(ev[first + i], y[i % 2])
+      e0.record()
+      exchange.step_prepared(prepared, y[i % 2], None, None)
+      e1.record()
+      torch.cuda.synchronize()
+      total += e0.elapsed_time(e1)
+    exchange.check()
+    return total
+
+  run(0, max(W, 1))
+  ms = run(W, K)
+  emit({'profiler_aid': f'one process standing in for rank 0 of {args.one_rank_of}: scatter half of the step', 'n_gpus': 1,
+        'steps': K, 'ms_per_step': ms / K, 'shard_columns': shape[1], 'synapses_on_device': int(work['indices'].numel()),
+        'block_width': prepared.block_width, 'n_blocks': prepared.n_blocks})
 
 
 def run_single(args, torch, device):
@@ -779,9 +819,11 @@ def main():
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
-  ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5'],
+  ap.add_argument('--config', default='c3', choices=['c1', 'c2', 'c3', 'c4', 'c5', 'a13'],
                   help='c3 (default) is the benchmark; the other configurations print their own JSON lines '
                        '(see bench_configs.py)')
+  ap.add_argument('--one-rank-of', type=int, default=1,
+                  help='profiler aid (1 GPU): run rank 0\'s shard of an N-rank job through the one-launch sharded step')
   ap.add_argument('--neurons', type=int, default=N_NEURONS,
                   help='reduced twin of the workload (multiple of 100000), for profiler captures only')
   args = ap.parse_args()

@@ -324,9 +324,45 @@ def bench_c5(args, device):
     dist.destroy_process_group()
 
 
+def bench_a13(args, device):
+  """The legacy scatter targets (compat operators) on C2's connectivity (1e5 x 1e5, 100 per row, 1e7 connections)
+  with 5 % of the pre-synaptic neurons firing, beside the reference's CUDA wrappers of the same names."""
+  c = workloads.config_c2()
+  n, nnz = c['shape'][0], c['data'].shape[0]
+  rng = np.random.default_rng(13)
+  events = torch.as_tensor(rng.random(n) < 0.05).to(device)
+  data, indices, indptr = (torch.as_tensor(c[k]).to(device) for k in ('data', 'indices', 'indptr'))
+  pre_ids = torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=device),
+                                    (indptr[1:] - indptr[:-1]).to(torch.int64))
+  values_pre = torch.as_tensor(rng.standard_normal(n).astype(np.float32)).to(device)
+  y, y_ref = torch.empty(n, device=device), torch.empty(n, device=device)
+  peak, src = _hbm_peak()
+  active = int(events.sum()) * 100
+  cases = [
+    ('gpu_csr_event_sum_heter_f32_i32', 'lib/gpu_event_sum.cu:50-117', [events, indices, indptr, data, y],
+     gpu_ops.build_csr_event_sum_descriptor(n, n), active, 8 * active + n + 8 * n),
+    ('gpu_coo_event_sum_heter_f32_i32', 'lib/gpu_event_sum.cu:140-206', [events, pre_ids, indices, data, y],
+     gpu_ops.build_coo_event_sum_descriptor(nnz, n), active, 8 * nnz + 8 * active + 8 * n),
+    ('gpu_coo_atomic_sum_heter_f32_i32', 'lib/gpu_atomic_sum.cu:39-97', [values_pre, pre_ids, indices, y],
+     gpu_ops.build_coo_atomic_sum_descriptor(nnz, n), nnz, 12 * nnz + 8 * n),
+  ]
+  for name, where, bufs, opaque, ops, nbytes in cases:
+    us = time_graph(lambda i: _lib.call(name, bufs, opaque, device=device), args.steps, args.warmup)
+    ref_bufs = bufs[:-1] + [y_ref]
+    if name.startswith('gpu_coo_atomic_sum'):      # the reference's wrapper reads the two id arrays the other way round
+      ref_bufs = [values_pre, indices, pre_ids, y_ref]
+    ref_us = reference_cuda_us(name, ref_bufs, opaque)
+    emit(config='a13 ' + name, metric='synaptic_ops_per_sec', value=ops / (us * 1e-6), unit='SyOp/s', us_per_call=us,
+         synaptic_ops_per_call=ops,
+         roofline={'bound': 'L2 reductions (hbm nominally)', 'achieved': nbytes / (us * 1e-6) / 1e9, 'peak': peak,
+                   'unit': 'GB/s', 'frac': nbytes / (us * 1e-6) / 1e9 / peak, 'peak_source': src,
+                   'algorithmic_bytes': nbytes},
+         reference_cuda=ref_cuda_entry(ref_us, where, us))
+
+
 def main(argv=None):
   ap = argparse.ArgumentParser()
-  ap.add_argument('config', choices=['c1', 'c2', 'c4', 'c5'])
+  ap.add_argument('config', choices=['c1', 'c2', 'c4', 'c5', 'a13'])
   ap.add_argument('--steps', type=int, default=None)
   ap.add_argument('--warmup', type=int, default=3)
   ap.add_argument('--variant', default=None, choices=[None, 'homo', 'uniform', 'normal'])
@@ -335,14 +371,14 @@ def main(argv=None):
   ap.add_argument('--cols', type=int, default=None, help='c5: number of output columns (default 65536)')
   args = ap.parse_args(argv)
   if args.steps is None:
-    args.steps = {'c1': 200, 'c2': 40, 'c4': 3, 'c5': 3}[args.config]
+    args.steps = {'c1': 200, 'c2': 40, 'c4': 3, 'c5': 3, 'a13': 20}[args.config]
   if not torch.cuda.is_available():
     raise SystemExit('a CUDA device is required (no CPU fallback)')
   _lib.lib()
   if 'LOCAL_RANK' in os.environ:
     torch.cuda.set_device(int(os.environ['LOCAL_RANK']))
   device = torch.device('cuda', torch.cuda.current_device())
-  {'c1': bench_c1, 'c2': bench_c2, 'c4': bench_c4, 'c5': bench_c5}[args.config](args, device)
+  {'c1': bench_c1, 'c2': bench_c2, 'c4': bench_c4, 'c5': bench_c5, 'a13': bench_a13}[args.config](args, device)
 
 
 if __name__ == '__main__':

@@ -449,24 +449,34 @@ jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double
 // memory, the same order of additions (same bits), with (position, weight) read from the list.
 //
 // Workspace of one chunk of C columns (C a multiple of MM_THREADS; the host walks the columns chunk by chunk):
-//   n_over u32 (+ padding to 256 B) | cnt u32[C] | pos u32[(C / 32) * cap * 32] | w T[(C / 32) * cap * 32]
-// Entry j of column c sits at ((c / 32) * cap + j) * 32 + c % 32: the 32 columns of a warp are interleaved, so a
-// warp that stores (or loads) entry j of all its columns touches one 128-byte line per array.
+//   n_over u32 (+ padding to 256 B) | cnt u32[C] | Xt T[k * m_pad] (X transposed, see below) | entries MMEntry<T>[C * stride]
+// Entry j of column c sits at c * stride + j (stride = cap + 1 rounded up to even), position and weight side by side (8 bytes for float, 16 for double),
+// and a column's list ends with an entry whose position is 0xffffffff: a
+// thread walks its own column's entries front to back at its own pace, so what matters is that consecutive
+// entries of ONE column share 32-byte sectors (the first touch of a sector fetches the next entries too); an
+// interleaved-by-warp layout was measured first and cost a sector per entry (7.1 ms instead of the inline 6.1).
 // cap = expected connections per column + 10 standard deviations + 16.  A column with more (never seen; the bound
 // is not a proof) is counted in n_over and recomputed whole by jit_matmat_kernel in its overflow-only mode, so the
 // result is exact whatever the draws.
+template<typename T> struct MMEntry;
+template<> struct __align__(8) MMEntry<float> { unsigned int pos; float w; };
+template<> struct __align__(16) MMEntry<double> { unsigned int pos, pad; double w; };
+template<typename T> struct __align__(16) MMEntryPair { MMEntry<T> a, b; };
+// slots per column: the entries, the terminating entry, rounded up to whole pairs
+__host__ __device__ inline unsigned int mm_list_stride(unsigned int cap) { return (cap + 2u) & ~1u; }
+
 template<typename T, int KIND>
 __global__ void __launch_bounds__(256)
 jit_matmat_fill_kernel(const unsigned int seed, const double log_p, const double w1, const double w2,
                        const unsigned int k, const unsigned int n, const unsigned int col0, const unsigned int cap,
-                       unsigned int *__restrict__ cnt, unsigned int *__restrict__ pos_list, T *__restrict__ w_list,
+                       unsigned int *__restrict__ cnt, MMEntry<T> *__restrict__ entries,
                        unsigned int *__restrict__ n_over) {
     const unsigned int c = blockIdx.x * 256u + threadIdx.x;     // column within the chunk
     const unsigned long long n_i64 = static_cast<unsigned long long>(col0) + c;
     if (n_i64 >= n) return;
     Stream s(seed + static_cast<unsigned int>(n_i64), log_p);
     curandState &st = s.st;
-    const size_t base = static_cast<size_t>(c >> 5) * cap * 32u + (c & 31u);
+    MMEntry<T> *mine = entries + static_cast<size_t>(c) * mm_list_stride(cap);
     unsigned int count = 0;
     unsigned int pos = s.ugap();
     while (pos < k) {
@@ -474,81 +484,167 @@ jit_matmat_fill_kernel(const unsigned int seed, const double log_p, const double
         if (KIND == W_NORMAL) rand = (T) (curand_normal(&st) * w2 + w1);
         else rand = (T) (curand_uniform(&st) * w2 + w1);
         if (count < cap) {
-            pos_list[base + static_cast<size_t>(count) * 32u] = pos;
-            w_list[base + static_cast<size_t>(count) * 32u] = rand;
+            MMEntry<T> e;
+            e.pos = pos;
+            e.w = rand;
+            mine[count] = e;
         }
         ++count;
         pos += s.ugap();
     }
     cnt[c] = count;
+    // the list ends with a position no tile contains; a list that overflowed reads as empty
+    MMEntry<T> last;
+    last.pos = 0xffffffffu;
+    last.w = T(0);
+    mine[count <= cap ? count : 0u] = last;
     if (count > cap) atomicAdd(n_over, 1u);
 }
 
-template<typename T> struct MMListTile;
-template<> struct MMListTile<float> { static constexpr int KT = 768; };    // 96 KB, two blocks per SM
-template<> struct MMListTile<double> { static constexpr int KT = 384; };
+// ---- the multiply ----
+// X is first transposed into the workspace (Xt[k][m_pad]): the values of a group of rows at position pos are then
+// contiguous, and a K-tile of a row group is copied into shared memory as is, by 16-byte asynchronous copies, while
+// the previous tile is being multiplied (two buffers).
+//
+// Mapping: a thread owns one column and 32 rows of X, as in the inline kernel, and walks its own list; the block is
+// one per SM with up to 1024 threads and two tiles of 768 positions (96 KB each).  What bounds it is the spread of
+// the number of connections per thread and tile (Poisson, mean 7.7 at C5): every tile ends at a block-wide barrier,
+// so the slowest thread sets its length, and shared memory caps the tile.  Measured alternatives, same workload
+// (inline kernel, generator included: 6.1 ms):
+//   * row-major X staged through registers, 512 threads, tiles of 768, two blocks per SM          6.2 ms
+//   * Xt tiles copied asynchronously, 512 threads, two tiles of 384, two blocks per SM            4.4 ms
+//   * lanes as rows (a warp owns 8-16 columns x 128 rows, every lane works on every connection, no spread at all):
+//     10 ms with a column's entry loaded when the column is visited, 7.7 ms with the next entry of every column kept
+//     in registers — a block then covers only 192 columns, so a staged tile is used by too few connections and the
+//     copies of Xt (22 GB instead of 4 GB) bound it.
+// Each (row, column) sum receives its products in stream order: same bits as the inline kernel.
+template<typename T> struct MMApply;
+template<> struct MMApply<float> { static constexpr int MAX_THREADS = 896; };      // up to 72 registers per thread
+template<> struct MMApply<double> { static constexpr int MAX_THREADS = 512; };     // 32 double sums: up to 128
+constexpr int MMA_TILE_BYTES = 96 * 1024;      // per buffer, two buffers, one block per SM
 
+__device__ __forceinline__ void mm_cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 :: "r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(__cvta_generic_to_global(src))
+                 : "memory");
+}
+
+// 32 x 32 tiles through shared memory; grid = (ceil(k / 32), m_pad / 32), block = (32, 8)
 template<typename T>
-__global__ void __launch_bounds__(MM_THREADS, (sizeof(T) == 8 ? 1 : 2))     // 32 double sums need more than 64 registers
-jit_matmat_apply_kernel(const T *__restrict__ X, const unsigned int m, const unsigned int k, const unsigned int n,
-                        const unsigned int col0, const unsigned int cap, const unsigned int *__restrict__ cnt,
-                        const unsigned int *__restrict__ pos_list, const T *__restrict__ w_list, T *__restrict__ Y) {
-    constexpr int KT = MMListTile<T>::KT, CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
+__global__ void __launch_bounds__(256)
+jit_matmat_transpose_kernel(const T *__restrict__ X, const unsigned int m, const unsigned int k,
+                            const unsigned int m_pad, T *__restrict__ Xt) {
+    __shared__ T t[32][33];
+    const unsigned int k0 = blockIdx.x * 32u, m0 = blockIdx.y * 32u;
+    for (unsigned int i = threadIdx.y; i < 32u; i += 8u) {
+        const unsigned int r = m0 + i, c = k0 + threadIdx.x;
+        t[i][threadIdx.x] = (r < m && c < k) ? X[static_cast<size_t>(r) * k + c] : T(0);
+    }
+    __syncthreads();
+    for (unsigned int i = threadIdx.y; i < 32u; i += 8u) {
+        const unsigned int c = k0 + i;
+        if (c < k) Xt[static_cast<size_t>(c) * m_pad + m0 + threadIdx.x] = t[threadIdx.x][i];
+    }
+}
+
+// grid = (row groups of 32, column blocks of blockDim.x columns): the blocks that walk the same columns' lists are
+// launched side by side, so the lists come from DRAM once and from L2 for the other row groups.
+template<typename T>
+__global__ void __launch_bounds__(MMApply<T>::MAX_THREADS, 1)
+jit_matmat_apply_kernel(const T *__restrict__ Xt, const unsigned int m, const unsigned int m_pad, const unsigned int k,
+                        const unsigned int n, const unsigned int col0, const unsigned int cols,
+                        const unsigned int cap, const unsigned int *__restrict__ cnt,
+                        const MMEntry<T> *__restrict__ entries, T *__restrict__ Y) {
+    constexpr int CHUNKS = MMTile<T>::CHUNKS, PER_CHUNK = 16 / sizeof(T);
+    constexpr int KT = MMA_TILE_BYTES / (MM_ROWS * static_cast<int>(sizeof(T)));   // positions per tile
+    constexpr int ROW_PIECES = MM_ROWS * sizeof(T) / 16;                           // 16-byte pieces per position
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T *tile = reinterpret_cast<T *>(smem_raw);   // [KT][MM_ROWS]
+    T *tiles = reinterpret_cast<T *>(smem_raw);   // [2][KT][MM_ROWS]
 
-    const unsigned int c = blockIdx.x * MM_THREADS + threadIdx.x;
-    const unsigned long long n_i64 = static_cast<unsigned long long>(col0) + c;
-    const bool live = n_i64 < n;
-    const unsigned int n_i = static_cast<unsigned int>(n_i64);
-    const unsigned int m_i = blockIdx.y * MM_ROWS;
-    const unsigned int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const bool vec_ok = (k % (16 / sizeof(T)) == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
+    const unsigned int c = blockIdx.y * blockDim.x + threadIdx.x;       // column within the chunk
+    const bool live = c < cols;
+    const unsigned int n_i = col0 + c;
+    const unsigned int m_i = blockIdx.x * MM_ROWS;
+    const unsigned int lane = threadIdx.x & 31;
 
-    const unsigned int stored = live ? cnt[c] : 0u;
-    const bool fits = stored <= cap;                 // else: the overflow pass writes this column
-    const unsigned int count = fits ? stored : 0u;
-    const size_t base = static_cast<size_t>(c >> 5) * cap * 32u + lane;
+    const bool fits = live && cnt[c] <= cap;                           // else: the overflow pass writes this column
+    // The list is read two entries at a time (one 16-byte load per lane every other connection: every lane reads its
+    // own list, so a warp's load touches 32 different lines and costs the load/store pipe as much as all shared loads
+    // of a connection together).  `cur` holds the pair being consumed, `nxt` the pair after it, requested when `cur`
+    // is entered; `j` counts consumed entries.
+    const MMEntryPair<T> *pairs =
+        reinterpret_cast<const MMEntryPair<T> *>(entries + static_cast<size_t>(c) * mm_list_stride(cap));
+    MMEntryPair<T> cur, nxt;
+    cur.a.pos = cur.b.pos = nxt.a.pos = nxt.b.pos = 0xffffffffu;
+    cur.a.w = cur.b.w = nxt.a.w = nxt.b.w = T(0);
     unsigned int j = 0;
-    unsigned int pos = count > 0 ? pos_list[base] : 0xffffffffu;
-    T rand = count > 0 ? w_list[base] : T(0);
+    if (live) {                                                         // an overflowed list reads as empty
+        cur = pairs[0];
+        if (cur.a.pos != 0xffffffffu && cur.b.pos != 0xffffffffu) nxt = pairs[1];
+    }
+    unsigned int pos = cur.a.pos;
+    T rand = cur.a.w;
     T sum[MM_ROWS];
 #pragma unroll
     for (int i = 0; i < MM_ROWS; ++i) sum[i] = 0;
 
-    for (unsigned int k0 = 0; k0 < k; k0 += KT) {
-        mm_stage_tile<T, KT>(tile, X, m_i, m, k, k0, vec_ok, lane, warp);
-        __syncthreads();
+    // tile t = positions [t * KT, min((t + 1) * KT, k)) of the row group, into buffer t & 1
+    auto issue = [&](unsigned int t) {
+        const unsigned int k0 = t * KT;
+        const unsigned int rows = min(static_cast<unsigned int>(KT), k - k0);
+        T *dst = tiles + static_cast<size_t>(t & 1u) * KT * MM_ROWS;
+        const T *src = Xt + static_cast<size_t>(k0) * m_pad + m_i;
+        for (unsigned int q = threadIdx.x; q < rows * ROW_PIECES; q += blockDim.x) {
+            const unsigned int kk = q / ROW_PIECES, piece = q % ROW_PIECES;
+            mm_cp_async16(dst + kk * MM_ROWS + piece * PER_CHUNK, src + static_cast<size_t>(kk) * m_pad + piece * PER_CHUNK);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const unsigned int n_tiles = (k + KT - 1) / KT;
+    issue(0);
+    for (unsigned int t = 0; t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) {
+            issue(t + 1);                                            // its buffer was last read in iteration t - 1
+            asm volatile("cp.async.wait_group 1;" ::: "memory");    // this thread's copies of tile t have landed
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                                             // everyone's have
+        const unsigned int k0 = t * KT;
         const unsigned int k_end = min(k0 + KT, k);
+        const T *tile = tiles + static_cast<size_t>(t & 1u) * KT * MM_ROWS;
         while (pos < k_end) {
-            // the next entry is requested before this one is applied
-            const unsigned int jn = j + 1;
-            const bool more = jn < count;
-            const unsigned int pos_n = more ? pos_list[base + static_cast<size_t>(jn) * 32u] : 0xffffffffu;
-            const T rand_n = more ? w_list[base + static_cast<size_t>(jn) * 32u] : T(0);
             const T *row = tile + (pos - k0) * MM_ROWS;
+            const T w = rand;
+            ++j;
+            if (j & 1u) {                                            // second entry of the pair
+                pos = cur.b.pos;
+                rand = cur.b.w;
+            } else {                                                 // next pair; request the one after it unless the
+                cur = nxt;                                           // list ends inside (position 0xffffffff ends it)
+                pos = cur.a.pos;
+                rand = cur.a.w;
+                if (cur.a.pos != 0xffffffffu && cur.b.pos != 0xffffffffu) nxt = pairs[(j >> 1) + 1];
+            }
 #pragma unroll
             for (int cc = 0; cc < CHUNKS; ++cc) {
                 const unsigned int chunk = (cc + lane) & (CHUNKS - 1);
                 if (sizeof(T) == 4) {
                     const float4 x = *reinterpret_cast<const float4 *>(row + chunk * PER_CHUNK);
-                    sum[cc * 4 + 0] += (x.x * rand);
-                    sum[cc * 4 + 1] += (x.y * rand);
-                    sum[cc * 4 + 2] += (x.z * rand);
-                    sum[cc * 4 + 3] += (x.w * rand);
+                    sum[cc * 4 + 0] += (x.x * w);
+                    sum[cc * 4 + 1] += (x.y * w);
+                    sum[cc * 4 + 2] += (x.z * w);
+                    sum[cc * 4 + 3] += (x.w * w);
                 } else {
                     const double2 x = *reinterpret_cast<const double2 *>(row + chunk * PER_CHUNK);
-                    sum[cc * 2 + 0] += (x.x * rand);
-                    sum[cc * 2 + 1] += (x.y * rand);
+                    sum[cc * 2 + 0] += (x.x * w);
+                    sum[cc * 2 + 1] += (x.y * w);
                 }
             }
-            j = jn;
-            pos = pos_n;
-            rand = rand_n;
         }
-        __syncthreads();
+        __syncthreads();                                             // tile t is free for the copies of tile t + 2
     }
-    if (live && fits) {
+    if (fits && static_cast<unsigned long long>(col0) + c < n) {
 #pragma unroll
         for (int cc = 0; cc < CHUNKS; ++cc) {
             const unsigned int chunk = (cc + lane) & (CHUNKS - 1);
@@ -710,17 +806,19 @@ size_t g_mm_list_budget_override = 0;
 struct MMListPlan {
     unsigned int cap;        // list slots per column
     unsigned int chunk;      // columns per chunk (multiple of MM_THREADS)
-    size_t cnt_off, pos_off, w_off, bytes;
+    unsigned int m_pad;      // rows of X rounded up to MM_ROWS
+    size_t cnt_off, xt_off, entries_off, bytes;
 };
 
-inline MMListPlan mm_list_plan(unsigned int k, unsigned int n, double log_p, size_t elem) {
+inline MMListPlan mm_list_plan(unsigned int m, unsigned int k, unsigned int n, double log_p, size_t elem) {
     MMListPlan p;
     const double prob = -expm1(log_p);                        // log_p = log(1 - conn_prob)
     const double mean = static_cast<double>(k) * prob;
     const double cap_d = ceil(mean + 10.0 * sqrt(mean * (1.0 - prob) + 1.0)) + 16.0;
     p.cap = static_cast<unsigned int>(cap_d < static_cast<double>(k) + 16.0 ? cap_d : static_cast<double>(k) + 16.0);
     if (g_mm_list_cap_override != 0) p.cap = g_mm_list_cap_override;
-    const size_t per_col = static_cast<size_t>(p.cap) * (4 + elem) + 4;
+    const size_t entry = elem == 8 ? 16 : 8;        // sizeof(MMEntry<T>)
+    const size_t per_col = static_cast<size_t>(mm_list_stride(p.cap)) * entry + 4;
     const size_t n_round = (static_cast<size_t>(n) + MM_THREADS - 1) / MM_THREADS * MM_THREADS;
     const size_t budget = g_mm_list_budget_override != 0 ? g_mm_list_budget_override : MM_LIST_BUDGET;
     size_t chunk = budget / per_col / MM_THREADS * MM_THREADS;
@@ -729,9 +827,10 @@ inline MMListPlan mm_list_plan(unsigned int k, unsigned int n, double log_p, siz
     p.chunk = static_cast<unsigned int>(chunk);
     auto up = [](size_t v) { return (v + 255) / 256 * 256; };
     p.cnt_off = 256;
-    p.pos_off = up(p.cnt_off + 4 * chunk);
-    p.w_off = up(p.pos_off + 4 * chunk * p.cap);
-    p.bytes = up(p.w_off + elem * chunk * p.cap);
+    p.m_pad = (m + MM_ROWS - 1) / MM_ROWS * MM_ROWS;
+    p.xt_off = up(p.cnt_off + 4 * chunk);
+    p.entries_off = up(p.xt_off + elem * static_cast<size_t>(k) * p.m_pad);
+    p.bytes = up(p.entries_off + entry * chunk * static_cast<size_t>(mm_list_stride(p.cap)));
     return p;
 }
 
@@ -752,8 +851,12 @@ void jit_matmat_list_impl(cudaStream_t stream, void **buffers, const char *opaqu
         set_status(BPL_ERR_ARGUMENT, "matmat: the workspace is missing or not aligned to 256 bytes");
         return;
     }
-    const MMListPlan p = mm_list_plan(d->k, d->n, d->log_p, sizeof(T));
-    constexpr size_t smem_apply = static_cast<size_t>(MMListTile<T>::KT) * MM_ROWS * sizeof(T);
+    if (d->k == 0) {
+        if (cudaMemsetAsync(Y, 0, sizeof(T) * static_cast<size_t>(d->m) * d->n, stream) != cudaSuccess) launch_ok();
+        return;
+    }
+    const MMListPlan p = mm_list_plan(d->m, d->k, d->n, d->log_p, sizeof(T));
+    constexpr size_t smem_apply = 2 * static_cast<size_t>(MMA_TILE_BYTES);
     constexpr size_t smem_inline = static_cast<size_t>(MMTile<T>::KT) * MM_ROWS * sizeof(T);
     static thread_local int configured_device = -1;
     int dev = 0;
@@ -770,8 +873,11 @@ void jit_matmat_list_impl(cudaStream_t stream, void **buffers, const char *opaqu
     }
     unsigned int *n_over = reinterpret_cast<unsigned int *>(ws);
     unsigned int *cnt = reinterpret_cast<unsigned int *>(ws + p.cnt_off);
-    unsigned int *pos_list = reinterpret_cast<unsigned int *>(ws + p.pos_off);
-    T *w_list = reinterpret_cast<T *>(ws + p.w_off);
+    MMEntry<T> *entries = reinterpret_cast<MMEntry<T> *>(ws + p.entries_off);
+    T *Xt = reinterpret_cast<T *>(ws + p.xt_off);
+    const unsigned int sms = static_cast<unsigned int>(sm_count());
+    jit_matmat_transpose_kernel<T><<<dim3(blocks_for(d->k, 32), p.m_pad / 32), dim3(32, 8), 0, stream>>>(
+        X, d->m, d->k, p.m_pad, Xt);
     for (unsigned long long col0 = 0; col0 < d->n; col0 += p.chunk) {
         const unsigned int cols = static_cast<unsigned int>(
             d->n - col0 < p.chunk ? d->n - col0 : static_cast<unsigned long long>(p.chunk));
@@ -781,10 +887,22 @@ void jit_matmat_list_impl(cudaStream_t stream, void **buffers, const char *opaqu
             return;
         }
         jit_matmat_fill_kernel<T, KIND><<<blocks_for(cols, 256), 256, 0, stream>>>(
-            d->seed, d->log_p, d->w1, d->w2, d->k, d->n, c0, p.cap, cnt, pos_list, w_list, n_over);
+            d->seed, d->log_p, d->w1, d->w2, d->k, d->n, c0, p.cap, cnt, entries, n_over);
         const dim3 grid(blocks_for(cols, MM_THREADS), gy);
-        jit_matmat_apply_kernel<T><<<grid, MM_THREADS, smem_apply, stream>>>(
-            X, d->m, d->k, d->n, c0, p.cap, cnt, pos_list, w_list, Y);
+        // threads per block (= columns per block): the size whose last wave of blocks, one per SM, wastes least
+        unsigned int threads = 128, best_cost = 0xffffffffu;
+        for (unsigned int th = 256; th <= static_cast<unsigned int>(MMApply<T>::MAX_THREADS); th += 128) {
+            const unsigned long long blocks = static_cast<unsigned long long>(blocks_for(cols, th)) * gy;
+            const unsigned long long waves = (blocks + sms - 1) / sms;
+            const unsigned long long cost = waves * th;
+            if (cost <= best_cost) {
+                best_cost = static_cast<unsigned int>(cost < 0xffffffffull ? cost : 0xfffffffeull);
+                threads = th;
+            }
+        }
+        const dim3 grid_apply(gy, blocks_for(cols, threads));
+        jit_matmat_apply_kernel<T><<<grid_apply, threads, smem_apply, stream>>>(Xt, d->m, p.m_pad, d->k, d->n, c0, cols,
+                                                                               p.cap, cnt, entries, Y);
         jit_matmat_kernel<T, KIND><<<grid, MM_THREADS, smem_inline, stream>>>(
             X, d->seed, d->log_p, d->w1, d->w2, d->m, d->k, d->n, Y, c0, cnt, p.cap, n_over);
     }
@@ -797,7 +915,7 @@ size_t matmat_list_workspace_bytes(const char *opaque, size_t opaque_len, size_t
     if (opaque == nullptr || opaque_len != sizeof(MatMatJITProbDescriptor1)) return 0;
     const MatMatJITProbDescriptor1 *d = reinterpret_cast<const MatMatJITProbDescriptor1 *>(opaque);
     if (d->n == 0) return 256;
-    return mm_list_plan(d->k, d->n, d->log_p, elem).bytes;
+    return mm_list_plan(d->m, d->k, d->n, d->log_p, elem).bytes;
 }
 
 }  // namespace bpl

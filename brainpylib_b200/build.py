@@ -63,10 +63,17 @@ def build(force=False, verbose=False):
   with concurrent.futures.ThreadPoolExecutor(max_workers=len(srcs)) as ex:
     results = list(ex.map(lambda s: _compile(s, verbose), srcs))
   objs = [o for o, _ in results]
-  info = ''.join(log for _, log in results)
-  if info:
-    with open(os.path.join(BUILD_DIR, 'ptxas_info.txt'), 'a') as f:
-      f.write(info)
+  # one log per source, replaced whenever that source is recompiled; ptxas_info.txt is their concatenation and so
+  # always describes the objects the library is linked from
+  for s, (_, log) in zip(srcs, results):
+    if log:
+      with open(os.path.join(BUILD_DIR, 'ptxas_' + os.path.splitext(s)[0] + '.txt'), 'w') as f:
+        f.write(log)
+  with open(os.path.join(BUILD_DIR, 'ptxas_info.txt'), 'w') as out:
+    for s in srcs:
+      part = os.path.join(BUILD_DIR, 'ptxas_' + os.path.splitext(s)[0] + '.txt')
+      if os.path.exists(part):
+        out.write(open(part).read())
   if force or _stale(LIB, objs):
     cmd = [NVCC, '-shared', '-o', LIB] + objs + ['-gencode', 'arch=compute_100a,code=sm_100a']
     if verbose:

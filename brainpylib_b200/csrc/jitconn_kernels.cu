@@ -366,7 +366,7 @@ __device__ __forceinline__ void mm_stage_tile(T *tile, const T *__restrict__ X, 
 }
 
 template<typename T, int KIND>
-__global__ void __launch_bounds__(MM_THREADS, 2)
+__global__ void __launch_bounds__(MM_THREADS, (sizeof(T) == 8 ? 1 : 2))     // 32 double sums: more than 64 registers
 jit_matmat_kernel(const T *__restrict__ X, const unsigned int seed, const double log_p, const double w1,
                   const double w2, const unsigned int m, const unsigned int k, const unsigned int n,
                   T *__restrict__ Y, const unsigned int col0 = 0, const unsigned int *__restrict__ cnt = nullptr,

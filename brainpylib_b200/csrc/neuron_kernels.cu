@@ -46,12 +46,19 @@ struct LifExpDescriptor {
 };
 static_assert(sizeof(LifExpDescriptor) == 76, "layout");
 
-__global__ void __launch_bounds__(SCAN_THREADS)
+// 1024 threads per 4096-neuron tile (4 neurons per thread, a warp covers 128 consecutive neurons): the kernel is a
+// stream of ~50 bytes per neuron and needs many loads in flight; with the spike scan's 256 threads per tile (16
+// neurons per thread) a million neurons kept only 13 warps per SM busy and ran at 2.5x its memory time.
+constexpr int LIF_THREADS = 1024;
+constexpr int LIF_PER_THREAD = SCAN_TILE / LIF_THREADS;          // 4
+constexpr int LIF_WARP_SPAN = 32 * LIF_PER_THREAD;               // 128
+
+__global__ void __launch_bounds__(LIF_THREADS)
 lif_exp_step_kernel(float *__restrict__ y, float *__restrict__ g, float *__restrict__ V, float *__restrict__ t_last,
                     float *__restrict__ spikes, const LifExpDescriptor d, const uint32_t chunk, const uint32_t n_chunks,
                     uint32_t *__restrict__ counts, uint32_t *__restrict__ ids) {
     if (blockIdx.x >= n_chunks) return;
-    __shared__ uint32_t warp_total[SCAN_THREADS / 32];
+    __shared__ uint32_t warp_total[LIF_THREADS / 32];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n = d.n;
     const uint64_t chunk_begin = static_cast<uint64_t>(blockIdx.x) * chunk;
@@ -59,10 +66,10 @@ lif_exp_step_kernel(float *__restrict__ y, float *__restrict__ g, float *__restr
     uint32_t *out = ids + chunk_begin;
     uint32_t running = 0;
     for (uint64_t tile = chunk_begin; tile < chunk_end; tile += SCAN_TILE) {
-        const uint64_t base = tile + static_cast<uint64_t>(warp) * SCAN_WARP_SPAN;
-        bool act[16];
+        const uint64_t base = tile + static_cast<uint64_t>(warp) * LIF_WARP_SPAN;
+        bool act[LIF_PER_THREAD];
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < LIF_PER_THREAD; ++k) {
             const uint64_t i = base + k * 32 + lane;
             act[k] = false;
             if (i < chunk_end) {
@@ -87,10 +94,10 @@ lif_exp_step_kernel(float *__restrict__ y, float *__restrict__ g, float *__restr
                 spikes[i] = spike ? 1.0f : 0.0f;
             }
         }
-        uint32_t bits[16];
+        uint32_t bits[LIF_PER_THREAD];
         uint32_t total = 0;
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < LIF_PER_THREAD; ++k) {
             bits[k] = __ballot_sync(FULL_MASK, act[k]);
             total += __popc(bits[k]);
         }
@@ -98,7 +105,7 @@ lif_exp_step_kernel(float *__restrict__ y, float *__restrict__ g, float *__restr
         __syncthreads();
         uint32_t offset = running, tile_total = 0;
 #pragma unroll
-        for (int w = 0; w < SCAN_THREADS / 32; ++w) {
+        for (int w = 0; w < LIF_THREADS / 32; ++w) {
             const uint32_t t = warp_total[w];
             if (w < static_cast<int>(warp)) offset += t;
             tile_total += t;
@@ -106,7 +113,7 @@ lif_exp_step_kernel(float *__restrict__ y, float *__restrict__ g, float *__restr
         __syncthreads();
         const uint32_t below = (1u << lane) - 1u;
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < LIF_PER_THREAD; ++k) {
             if (act[k]) out[offset + __popc(bits[k] & below)] = static_cast<uint32_t>(base + k * 32 + lane);
             offset += __popc(bits[k]);
         }
@@ -153,7 +160,7 @@ void lif_exp_step_float(bpl_stream_t stream, void **buffers, const char *opaque,
     uint32_t *list = static_cast<uint32_t *>(buffers[5]);
     const ScanPlan p = plan_scan(d->n);
     if (d->n == 0) return;
-    lif_exp_step_kernel<<<p.n_chunks, SCAN_THREADS, 0, stream>>>(
+    lif_exp_step_kernel<<<p.n_chunks, LIF_THREADS, 0, stream>>>(
         static_cast<float *>(buffers[0]), static_cast<float *>(buffers[1]), static_cast<float *>(buffers[2]),
         static_cast<float *>(buffers[3]), static_cast<float *>(buffers[4]), *d, p.chunk, p.n_chunks, list,
         list + MAX_CHUNKS);

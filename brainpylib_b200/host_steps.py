@@ -19,15 +19,20 @@ def _pinned(t, what):
 
 
 def _ring(tensors):
-  return (ctypes.c_void_p * 3)(*[t.data_ptr() for t in tensors])
+  return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
 
 class HostSteps:
   """``matrix``: ``(data, indices, indptr)`` of a CSR matrix on the GPU, or a
   :class:`brainpylib_b200.event_ops.ColumnBlockedCSR` made from one; ``events_dtype``: bool or float32."""
 
-  def __init__(self, matrix, *, shape, events_dtype=torch.float32):
+  def __init__(self, matrix, *, shape, events_dtype=torch.float32, group=3):
+    """``group``: steps between cross-stream synchronisation points (1..16); the device rings hold ``3 * group``
+    spike, result and workspace buffers."""
     n_row, n_col = int(shape[0]), int(shape[1])
+    if not 1 <= int(group) <= 16:
+      raise ValueError('group must be in 1..16')
+    self.group = int(group)
     if events_dtype not in (torch.bool, torch.float32):
       raise ValueError('events must be bool or float32')
     suffix = 'bool' if events_dtype == torch.bool else 'float'
@@ -53,10 +58,11 @@ class HostSteps:
       if t.device != device or not t.is_contiguous():
         raise ValueError('the matrix must be contiguous and on one device')
     self.device, self.shape, self.events_dtype, self._fixed = device, (n_row, n_col), events_dtype, fixed
-    self._ev = [torch.empty(n_row, dtype=events_dtype, device=device) for _ in range(3)]
-    self._y = [torch.empty(n_col, dtype=torch.float32, device=device) for _ in range(3)]
+    ring = 3 * self.group
+    self._ev = [torch.empty(n_row, dtype=events_dtype, device=device) for _ in range(ring)]
+    self._y = [torch.empty(n_col, dtype=torch.float32, device=device) for _ in range(ring)]
     ws_bytes = _lib.workspace_bytes(self.name, self.opaque)
-    self._ws = [torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device) for _ in range(3)]
+    self._ws = [torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device) for _ in range(ring)]
     self._streams = [torch.cuda.Stream(device) for _ in range(3)]
     n = len(fixed)
     self._buffers = (ctypes.c_void_p * (n + 3))(*[t.data_ptr() for t in fixed], self._ev[0].data_ptr(),
@@ -65,9 +71,9 @@ class HostSteps:
     self._fn = _lib.lib().bpl_run_host_steps
     self._fn.restype = None
     self._fn.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
-                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-                         ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32, ctypes.c_uint32,
-                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32,
+                         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32,
+                         ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
 
   def run(self, host_events: torch.Tensor, host_out: torch.Tensor) -> float:
     """``host_events``: ``(n_steps, n_row)`` pinned; ``host_out``: ``(slots, n_col)`` pinned float32, step ``s`` lands
@@ -87,7 +93,7 @@ class HostSteps:
       e0.record(s_c)
       n = self._n
       self._fn(self.name.encode(), self.opaque, len(self.opaque), self._buffers, n + 3, n, n + 1, n + 2, _ring(self._ev),
-               _ring(self._y), _ring(self._ws), host_events.data_ptr(), host_events.shape[1] * host_events.element_size(),
+               _ring(self._y), _ring(self._ws), self.group, host_events.data_ptr(), host_events.shape[1] * host_events.element_size(),
                host_out.data_ptr(), n_col * 4, host_out.shape[0], host_events.shape[0], s_in.cuda_stream, s_c.cuda_stream,
                s_out.cuda_stream)
       e1.record(s_c)

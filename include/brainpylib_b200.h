@@ -345,20 +345,22 @@ void bpl_sharded_cb_step(bpl_stream_t stream, const void *groups, const void *of
  * the call brackets the run.  host_in: n_steps x in_bytes; host_out: out_slots x out_bytes (step i lands in slot
  * i % out_slots).
  * bpl_run_host_steps: target_name (any registered target) is called once per step with buffers[in_index],
- * buffers[out_index] and, if ws_index >= 0, buffers[ws_index] replaced by in_ring / out_ring / ws_ring[step % 3]. */
+ * buffers[out_index] and, if ws_index >= 0, buffers[ws_index] replaced by a buffer of in_ring / out_ring / ws_ring,
+ * which hold 3 * group buffers each; cross-stream waits sit between groups of `group` (1..16) consecutive steps, the
+ * copies of a group run back to back. */
 void bpl_run_host_steps(const char *target_name, const char *opaque, size_t opaque_len, void *const *buffers,
                         int n_buffers, int in_index, int out_index, int ws_index, void *const *in_ring,
-                        void *const *out_ring, void *const *ws_ring, const void *host_in, size_t in_bytes,
-                        void *host_out, size_t out_bytes, uint32_t out_slots, uint32_t n_steps, bpl_stream_t s_in,
-                        bpl_stream_t s_compute, bpl_stream_t s_out);
+                        void *const *out_ring, void *const *ws_ring, uint32_t group, const void *host_in,
+                        size_t in_bytes, void *host_out, size_t out_bytes, uint32_t out_slots, uint32_t n_steps,
+                        bpl_stream_t s_in, bpl_stream_t s_compute, bpl_stream_t s_out);
 /* bpl_sharded_prime, then bpl_sharded_cb_step per step: host_events holds n_steps slices of this rank's own n_local
  * spike sources (float32 if ev_is_float, else one byte each), host_out takes this rank's n_out float32 outputs per
- * step; ev_ring[3]: n_local events each, y_ring[3]: n_out floats each (device). */
+ * step; ev_ring: 3 * group + 1 buffers of n_local events, y_ring: 3 * group buffers of n_out floats (device). */
 void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_t n_out, uint32_t block_width,
                                 int fixed_point, int scale_log2, uint32_t team_lanes_log2, int ev_is_float,
                                 uint32_t n_local, uint32_t row_offset, void *const *peer_lists, size_t slot_bytes,
                                 void *const *peer_flags, void *state, int world, int rank, int slots,
-                                uint32_t max_polls, void *const *ev_ring, void *const *y_ring,
+                                uint32_t max_polls, void *const *ev_ring, void *const *y_ring, uint32_t group,
                                 const void *host_events, void *host_out, uint32_t out_slots, uint32_t n_steps,
                                 bpl_stream_t s_in, bpl_stream_t s_compute, bpl_stream_t s_out);
 

@@ -20,9 +20,9 @@ def _case(shape, density, seed, cuda):
   return tuple(torch.as_tensor(a).to(cuda) for a in (data, indices, indptr)), rng
 
 
-@pytest.mark.parametrize('layout', ['csr', 'prepared', 'prepared_fixed', 'homo'])
+@pytest.mark.parametrize('layout,group', [('csr', 4), ('prepared', 4), ('prepared_fixed', 1), ('homo', 16), ('csr', 3)])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bool])
-def test_host_steps_match_the_operator_step_by_step(cuda, layout, dtype):
+def test_host_steps_match_the_operator_step_by_step(cuda, layout, group, dtype):
   import brainpylib_b200 as bpl
   shape = (20000, 7000)
   (d, ix, ptr), rng = _case(shape, 0.004, 41, cuda)
@@ -36,7 +36,8 @@ def test_host_steps_match_the_operator_step_by_step(cuda, layout, dtype):
   if layout.startswith('prepared'):
     prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=shape, block_width=2048,
                                          accumulate='fixed' if layout.endswith('fixed') else 'float')
-  runner = bpl.HostSteps(prepared if prepared is not None else (d, ix, ptr), shape=shape, events_dtype=dtype)
+  runner = bpl.HostSteps(prepared if prepared is not None else (d, ix, ptr), shape=shape, events_dtype=dtype,
+                         group=group)
   ms = runner.run(ev, out)
   assert ms > 0
   for s in range(steps):
@@ -65,8 +66,9 @@ def test_host_steps_refuse_pageable_memory_and_wrong_shapes(cuda):
   assert float(good_out.abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize('dtype,accumulate', [(torch.float32, 'float'), (torch.bool, 'fixed')])
-def test_sharded_host_steps_on_one_rank(cuda, dtype, accumulate):
+@pytest.mark.parametrize('dtype,accumulate,group', [(torch.float32, 'float', 4), (torch.bool, 'fixed', 1),
+                                                    (torch.float32, 'fixed', 5), (torch.bool, 'float', 16)])
+def test_sharded_host_steps_on_one_rank(cuda, dtype, accumulate, group):
   """world = 1: prime, one launch per step and the three-stream pipeline, against the operator step by step."""
   import brainpylib_b200 as bpl
   from brainpylib_b200 import sharded
@@ -79,7 +81,7 @@ def test_sharded_host_steps_on_one_rank(cuda, dtype, accumulate):
   ev = (ev if dtype == torch.bool else ev.float()).pin_memory()
   out = torch.full((steps, shape[1]), float('nan')).pin_memory()
   for _ in range(2):            # a second run continues on the same exchange object
-    ms = ex.run_host_steps(prepared, ev, out)
+    ms = ex.run_host_steps(prepared, ev, out, group=group)
     ex.check()
     assert ms > 0
     for s in range(steps):

@@ -113,6 +113,22 @@ __device__ __forceinline__ void cb_add(float *acc, const uint32_t c, const uint3
     }
 }
 
+// float accumulation of a group whose weights are scaled by the row's factor (dense vector product)
+__device__ __forceinline__ void cb_add_scaled(float *acc, const uint32_t c, const uint32_t w_bits, const float scale) {
+    const float w = __uint_as_float(w_bits);
+    if (w != 0.0f) atomicAdd(acc + c, w * scale);
+}
+__device__ __forceinline__ void cb_add_group_scaled(float *acc, const CbGroup &g, const float s) {
+    cb_add_scaled(acc, g.cc.x & 0xffffu, g.wa.x, s);
+    cb_add_scaled(acc, g.cc.x >> 16, g.wa.y, s);
+    cb_add_scaled(acc, g.cc.y & 0xffffu, g.wa.z, s);
+    cb_add_scaled(acc, g.cc.y >> 16, g.wa.w, s);
+    cb_add_scaled(acc, g.cc.z & 0xffffu, g.wb.x, s);
+    cb_add_scaled(acc, g.cc.z >> 16, g.wb.y, s);
+    cb_add_scaled(acc, g.cc.w & 0xffffu, g.wb.z, s);
+    cb_add_scaled(acc, g.cc.w >> 16, g.wb.w, s);
+}
+
 template<bool FIXED>
 __device__ __forceinline__ void cb_add_group(float *acc, const CbGroup &g) {
     cb_add<FIXED>(acc, g.cc.x & 0xffffu, g.wa.x);
@@ -126,14 +142,17 @@ __device__ __forceinline__ void cb_add_group(float *acc, const CbGroup &g) {
 }
 
 // Lane `lane` adds the group in its slot of a ring buffer into the slice (when its team filled that slot).
-template<bool FIXED>
-__device__ __forceinline__ void cb_accumulate(float *acc, const unsigned char *buf, const bool filled, const uint32_t lane) {
+// DENSE: the weights are multiplied by `scale`, the vector entry of the row the group belongs to.
+template<bool FIXED, bool DENSE = false>
+__device__ __forceinline__ void cb_accumulate(float *acc, const unsigned char *buf, const bool filled, const uint32_t lane,
+                                              const float scale = 1.0f) {
     if (filled) {
         CbGroup grp;
         grp.wa = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES);
         grp.wb = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 16);
         grp.cc = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 32);
-        cb_add_group<FIXED>(acc, grp);
+        if (DENSE) cb_add_group_scaled(acc, grp, scale);
+        else cb_add_group<FIXED>(acc, grp);
     }
 }
 
@@ -184,14 +203,18 @@ __device__ __forceinline__ void cb_stamp(unsigned long long *trace, const uint32
 //   counts / ids: the spike list (chunk_prefix / list_row layout); y: this matrix's output, already zero.
 //   smem: dynamic shared memory laid out by cb_plan; prefix / warp_total: static shared memory.
 //   inv_scale: FIXED only, 2^-k.
-template<int NBUF, bool FIXED, int LOG_L>
+//   DENSE (with x): y = A^T x for a dense vector x instead of a spike list: every row whose x is not zero is walked and
+//   its weights are multiplied by x[row] (float accumulation only); counts / ids are not read, n_chunks = n_row.
+template<int NBUF, bool FIXED, int LOG_L, bool DENSE = false>
 __device__ __forceinline__ void
 cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets, const uint32_t n_col,
                 const uint32_t width, const uint32_t n_blocks, const uint32_t b, const uint32_t p, const uint32_t P,
                 const uint32_t chunk, const uint32_t n_chunks, const uint32_t *__restrict__ counts,
                 const uint32_t *__restrict__ ids, float *__restrict__ y, const uint32_t acc_bytes,
                 unsigned char *smem, uint32_t *prefix, uint32_t *warp_total, const float inv_scale,
-                unsigned long long *trace = nullptr, const uint32_t trace_cta = 0) {
+                unsigned long long *trace = nullptr, const uint32_t trace_cta = 0, const float *__restrict__ x = nullptr) {
+    static_assert(!(DENSE && FIXED), "the dense product accumulates in float");
+    static_assert(NBUF <= 3, "the per-round scale registers cover three rounds in flight");
     constexpr uint32_t L = 1u << LOG_L, TEAMS = 32u / L;          // lanes (= slots) per team, teams per warp
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t team = lane >> LOG_L, sub = lane & (L - 1u);
@@ -208,33 +231,47 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     }
     for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = 0.0f;
 
-    const uint32_t n_act = cb_chunk_prefix(counts, n_chunks, prefix, warp_total);   // ends with a barrier
+    uint32_t n_act;
+    if (DENSE) {
+        n_act = n_chunks;
+        __syncthreads();                                                             // the slice is zero
+    } else {
+        n_act = cb_chunk_prefix(counts, n_chunks, prefix, warp_total);               // ends with a barrier
+    }
     if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 1);
     const uint32_t mine = n_act > p ? (n_act - p + P - 1) / P : 0;               // the CTA's rows: p, p + P, ...
     const uint32_t K = mine > warp ? (mine - warp + 31u) / 32u : 0u;             // this warp's: warp, warp + 32, ... of those
     const uint64_t stride = static_cast<uint64_t>(n_blocks) + 1;
 
     // lane `l` resolves the warp's row k: where its segment for block b starts and how many groups it has
-    auto resolve = [&](const uint32_t k, uint32_t &src, uint32_t &rem) {
+    auto resolve = [&](const uint32_t k, uint32_t &src, uint32_t &rem, float &xs) {
         src = 0;
         rem = 0;
+        xs = 0.0f;
         if (k < K) {
-            const uint32_t row = list_row(prefix, n_chunks, chunk, ids, p + (warp + 32u * k) * P);
-            const uint32_t *o = offsets + row * stride + b;
-            src = o[0];
-            rem = o[1] - src;
+            const uint32_t at = p + (warp + 32u * k) * P;
+            const uint32_t row = DENSE ? at : list_row(prefix, n_chunks, chunk, ids, at);
+            if (DENSE) xs = x[row];
+            if (!DENSE || xs != 0.0f) {                          // a row whose vector entry is zero adds nothing
+                const uint32_t *o = offsets + row * stride + b;
+                src = o[0];
+                rem = o[1] - src;
+            }
         }
     };
 
     uint32_t next_src, next_rem;
-    resolve(lane, next_src, next_rem);
+    float next_xs;
+    resolve(lane, next_src, next_rem, next_xs);
     if (trace != nullptr && threadIdx.x == 0 && next_rem != 0xffffffffu) cb_stamp(trace, trace_cta, 2);
     uint32_t issued = 0, consumed = 0;     // rounds committed / accumulated; buffer of round r is r % NBUF
     uint32_t pieces = 0;                   // groups this lane's team copied in the rounds in flight, 8 bits each, oldest lowest
+    float sc0 = 1.0f, sc1 = 1.0f, sc2 = 1.0f;   // DENSE: the vector entries of the rows of those rounds, oldest first
 
     for (uint32_t k0 = 0; k0 < K; k0 += 32u) {
         uint32_t src = next_src, rem = next_rem;
-        resolve(k0 + 32u + lane, next_src, next_rem);      // in flight while this batch streams
+        const float xs = next_xs;
+        resolve(k0 + 32u + lane, next_src, next_rem, next_xs);      // in flight while this batch streams
         uint32_t mask = __ballot_sync(FULL_MASK, rem > 0);
         while (mask) {
             // one round: team t copies up to L groups of the segment held by lane first + t into its own slots
@@ -260,13 +297,20 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
                 rem -= taken;
             }
             pieces |= piece << (8u * (issued - consumed));
+            if (DENSE) {
+                const float o_xs = __shfl_sync(FULL_MASK, xs, owner & 31u);
+                const uint32_t d = issued - consumed;
+                if (d == 0u) sc0 = o_xs; else if (d == 1u) sc1 = o_xs; else sc2 = o_xs;
+            }
             ++issued;
             if (issued - consumed == NBUF) {                // ring full: accumulate the oldest round
                 cp_async_wait<NBUF - 1>();
                 __syncwarp();
-                cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane);
+                cb_accumulate<FIXED, DENSE>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane, sc0);
                 __syncwarp();
                 pieces >>= 8;
+                sc0 = sc1;
+                sc1 = sc2;
                 ++consumed;
             }
             mask = __ballot_sync(FULL_MASK, rem > 0);
@@ -275,8 +319,10 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     cp_async_wait<0>();
     __syncwarp();
     while (consumed < issued) {
-        cb_accumulate<FIXED>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane);
+        cb_accumulate<FIXED, DENSE>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane, sc0);
         pieces >>= 8;
+        sc0 = sc1;
+        sc1 = sc2;
         ++consumed;
     }
     if (trace != nullptr && lane == 0) {

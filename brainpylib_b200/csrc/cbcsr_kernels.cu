@@ -52,6 +52,35 @@ event_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t
                                         blockIdx.x);
 }
 
+// y = A^T x for a dense float vector x on the same storage: every row with x[row] != 0 is walked, weights scaled by x[row].
+template<int NBUF, int LOG_L>
+__global__ void __launch_bounds__(CB_THREADS, 1)
+dense_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets,
+                        const uint32_t n_row, const uint32_t n_col, const uint32_t width, const uint32_t n_blocks,
+                        const uint32_t P, const float *__restrict__ x, float *__restrict__ y, const uint32_t acc_bytes) {
+    extern __shared__ __align__(128) unsigned char cb_smem[];
+    __shared__ uint32_t prefix[2];            // unused by the dense walk
+    __shared__ uint32_t warp_total[CB_WARPS];
+    cb_scatter_body<NBUF, false, LOG_L, true>(groups, offsets, n_col, width, n_blocks, blockIdx.x / P, blockIdx.x % P, P, 0,
+                                              n_row, nullptr, nullptr, y, acc_bytes, cb_smem, prefix, warp_total, 1.0f,
+                                              nullptr, 0, x);
+}
+
+using CbDenseKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
+                               const float *, float *, uint32_t);
+template<int NBUF>
+CbDenseKernel cb_dense_kernel_for_lanes(uint32_t log_l) {
+    switch (log_l) {
+        case 3: return dense_cb_scatter_kernel<NBUF, 3>;
+        case 4: return dense_cb_scatter_kernel<NBUF, 4>;
+        case 5: return dense_cb_scatter_kernel<NBUF, 5>;
+        default: return dense_cb_scatter_kernel<NBUF, 2>;
+    }
+}
+CbDenseKernel cb_dense_kernel(uint32_t n_buf, uint32_t log_l) {
+    return n_buf == 3 ? cb_dense_kernel_for_lanes<3>(log_l) : cb_dense_kernel_for_lanes<2>(log_l);
+}
+
 using CbKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
                           const uint32_t *, const uint32_t *, float *, uint32_t, float, unsigned long long *);
 
@@ -90,7 +119,7 @@ bool cb_kernel_configured() {
 // CTAs that share one column block (each takes every P-th active row), so that all SMs work.
 inline uint32_t cb_shares(uint32_t n_blocks) {
     const uint32_t P = static_cast<uint32_t>(sm_count()) / (n_blocks ? n_blocks : 1u);
-    return P < 1 ? 1u : (P > 16 ? 16u : P);
+    return P < 1 ? 1u : (P > 32 ? 32u : P);
 }
 
 // E = void: the spike list is an operand (buffers [groups, offsets, list, y]; y must already be zero) instead of
@@ -161,12 +190,81 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     launch_ok();
 }
 
+void cbcsr_matvec_transpose_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+    const CbDescriptor *d = unpack<CbDescriptor>(opaque, opaque_len);
+    if (!d) return;
+    const uint32_t n_row = d->n_row, n_col = d->n_col, width = d->block_width;
+    if (d->fixed_point != 0) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: the dense-vector product needs float weights (not fixed point)");
+        return;
+    }
+    if (width == 0 || width > CB_MAX_WIDTH || (width & 31u) != 0) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width must be a multiple of 32 in 32..32256");
+        return;
+    }
+    if (d->team_lanes_log2 != 0 && (d->team_lanes_log2 < 2 || d->team_lanes_log2 > 5)) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: team_lanes_log2 must be 2..5");
+        return;
+    }
+    if (n_col == 0) return;
+    const uint32_t n_blocks = (n_col + width - 1) / width;
+    if (n_blocks > CB_MAX_BLOCKS) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: more than 1024 column blocks");
+        return;
+    }
+    const unsigned char *groups = static_cast<const unsigned char *>(buffers[0]);
+    const uint32_t *offsets = static_cast<const uint32_t *>(buffers[1]);
+    const float *x = static_cast<const float *>(buffers[2]);
+    float *y = static_cast<float *>(buffers[3]);
+    if (!aligned16(groups)) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: the group array must be 16-byte aligned");
+        return;
+    }
+    if (cudaMemsetAsync(y, 0, sizeof(float) * static_cast<size_t>(n_col), stream) != cudaSuccess) {
+        launch_ok();
+        return;
+    }
+    if (n_row == 0) return;
+    const CbPlan plan = cb_plan(width);
+    if (!plan.ok) {
+        set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: block_width leaves no shared memory for the copy buffers");
+        return;
+    }
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        for (uint32_t n_buf = 2; n_buf <= 3; ++n_buf)
+            for (uint32_t log_l = 2; log_l <= 5; ++log_l)
+                if (cudaFuncSetAttribute(cb_dense_kernel(n_buf, log_l), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(CB_SMEM_LIMIT)) != cudaSuccess) {
+                    launch_ok();
+                    return;
+                }
+        configured_device = dev;
+    }
+    const uint32_t P = cb_shares(n_blocks);
+    const uint32_t log_l = d->team_lanes_log2 == 0 ? 2u : d->team_lanes_log2;
+    if (profile_before()) cudaEventRecord(profile_before(), stream);
+    cb_dense_kernel(plan.n_buf, log_l)<<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(
+        groups, offsets, n_row, n_col, width, n_blocks, P, x, y, plan.acc_bytes);
+    if (profile_after()) cudaEventRecord(profile_after(), stream);
+    launch_ok();
+}
+
 }  // namespace
 }  // namespace bpl
 
 using namespace bpl;
 
 extern "C" {
+
+// y = A^T x for a dense float32 vector x on the column-blocked storage (no counterpart in the reference, which takes
+// this product from cuSPARSE): buffers [groups, offsets, x f32(n_row), y f32(n_col)]; opaque as event_cbcsr_matvec_*
+// with fixed_point = 0.
+void cbcsr_matvec_transpose_heter_float(bpl_stream_t s, void **b, const char *o, size_t n) {
+    cbcsr_matvec_transpose_impl(s, b, o, n);
+}
 
 void event_cbcsr_matvec_heter_float_bool(bpl_stream_t s, void **b, const char *o, size_t n) {
     event_cbcsr_impl<uint8_t>(s, b, o, n);

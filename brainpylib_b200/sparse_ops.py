@@ -113,6 +113,58 @@ class _CSRMatvec(torch.autograd.Function):
     return loop_vmap(_CSRMatvec.apply, info, in_dims, (data, indices, indptr, vector, shape, transpose, method))
 
 
+def cbcsr_matvec_transpose_raw(prepared, vector, *, out=None):
+  """``y = A^T x`` on a matrix converted once with ``event_ops.csr_to_column_blocked`` (float accumulation); target
+  ``cbcsr_matvec_transpose_heter_float``.  No counterpart in the reference."""
+  from . import event_ops
+  n_row, n_col = prepared.shape
+  if prepared.scale_log2 is not None:
+    raise ValueError('the dense-vector product needs a matrix prepared with accumulate=\'float\'')
+  if vector.dtype != torch.float32 or vector.shape != (n_row,):
+    raise ValueError(f'vector must be float32 of shape ({n_row},)')
+  opaque = event_ops._cb_descriptor(n_row, n_col, prepared.block_width, None, prepared.team_lanes_log2)
+  if out is None:
+    out = torch.empty(n_col, dtype=torch.float32, device=vector.device)
+  _lib.call('cbcsr_matvec_transpose_heter_float', [prepared.groups, prepared.offsets, vector, out], opaque,
+            device=vector.device)
+  return out
+
+
+class _CSRMatvecPrepared(torch.autograd.Function):
+  """``y = A^T x`` on the prepared matrix.  Linear in ``x``: reverse mode is ``A ct`` on the CSR arrays, forward mode
+  the same product on the tangent; the prepared weights are constants (no gradient w.r.t. ``data``)."""
+
+  @staticmethod
+  def forward(data, indices, indptr, vector, shape, prepared):
+    return cbcsr_matvec_transpose_raw(prepared, vector)
+
+  @staticmethod
+  def setup_context(ctx, inputs, output):
+    data, indices, indptr, _vector, shape, prepared = inputs
+    ctx.save_for_backward(data, indices, indptr)
+    ctx.save_for_forward(data, indices, indptr)
+    ctx.shape, ctx.prepared = shape, prepared
+
+  @staticmethod
+  def backward(ctx, ct):
+    data, indices, indptr = ctx.saved_tensors
+    g_vec = None
+    if ctx.needs_input_grad[3]:
+      g_vec = _CSRMatvec.apply(data, indices, indptr, contiguous(ct), ctx.shape, False, 'vector')
+    return None, None, None, g_vec, None, None
+
+  @staticmethod
+  def jvp(ctx, _data_dot, _indices, _indptr, vector_dot, _shape, _prepared):
+    if vector_dot is None:
+      return None
+    data, indices, indptr = ctx.saved_tensors
+    return _CSRMatvecPrepared.apply(data, indices, indptr, contiguous(vector_dot), ctx.shape, ctx.prepared)
+
+  @staticmethod
+  def vmap(info, in_dims, data, indices, indptr, vector, shape, prepared):
+    return loop_vmap(_CSRMatvecPrepared.apply, info, in_dims, (data, indices, indptr, vector, shape, prepared))
+
+
 def _prepare(data, indices, indptr, vector):
   device = device_of(data, indices, indptr, vector)
   data = torch.atleast_1d(as_tensor(data, device))
@@ -137,7 +189,8 @@ def csr_matvec(
     *,
     shape: Tuple[int, int],
     method: str = 'vector',
-    transpose: bool = False
+    transpose: bool = False,
+    prepared=None
 ) -> torch.Tensor:
   """CSR sparse matrix product with a dense vector.
 
@@ -158,6 +211,11 @@ def csr_matvec(
     They name the same kernel here; an unknown name raises ``ValueError``.
   transpose: bool
     Whether to transpose the sparse matrix before computing.
+  prepared: ColumnBlockedCSR, optional
+    Not in the reference.  With ``transpose=True`` and float32 heterogeneous weights: the same matrix converted once
+    with ``event_ops.csr_to_column_blocked`` (float accumulation); the product then accumulates in shared memory
+    instead of through one L2 reduction per stored entry.  Same result up to the order of float32 additions; the
+    weights inside ``prepared`` are constants for differentiation.
 
   Returns
   -------
@@ -178,6 +236,14 @@ def csr_matvec(
     raise ValueError(f'shape {shape} does not match the given indptr {tuple(indptr.shape)}.')
   if vector.shape[0] != (shape[0] if transpose else shape[1]):
     raise ValueError(f'shape {shape} does not match the given vector {tuple(vector.shape)}.')
+  if prepared is not None:
+    if not transpose or data.dtype != torch.float32 or data.shape[0] == 1:
+      raise ValueError('prepared= applies to transpose=True with float32 heterogeneous weights')
+    if tuple(prepared.shape) != (int(shape[0]), int(shape[1])):
+      raise ValueError(f'the prepared matrix has shape {prepared.shape}, not {tuple(shape)}')
+    data, indices, indptr, vector = map(contiguous, (data, indices, indptr, vector))
+    return _CSRMatvecPrepared.apply(data, indices.to(torch.int32), indptr.to(torch.int32), vector,
+                                    (int(shape[0]), int(shape[1])), prepared)
   return _dispatch(data, indices, indptr, vector, shape, transpose, method)
 
 

@@ -118,6 +118,11 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   buffers [groups u8(48 * n_groups), offsets u32(n_row, n_blocks + 1), events E(n_row), y f32(n_col), workspace]
  *   workspace: bpl_workspace_bytes() (as for event_csr_matvec with transpose)
  *
+ * cbcsr_matvec_transpose_heter_float   (no counterpart in the reference, which takes this product from cuSPARSE)
+ *   y = A^T x for a dense float32 vector x on the same storage: every row with x[row] != 0 is walked and its weights
+ *   are multiplied by x[row]; float accumulation (fixed_point must be 0).
+ *   buffers [groups, offsets, x f32(n_row), y f32(n_col)]; opaque as above
+ *
  * event_cbcsr_matvec_list_heter_float / event_csr_matvec_list_heter_float   (no counterpart in the reference)
  *   the scatter half alone, driven by a ready-made spike list (counts[1024], then row ids in chunk segments: the
  *   layout of the event_csr_matvec workspace, written e.g. by lif_exp_step_float); y must already be zero.
@@ -242,6 +247,7 @@ void bpl_profile_scatter_events(void *before, void *after);
     X(gpu_matmat_prob_prob_normal_double_v3)                        \
     X(gpu_matmat_prob_prob_uniform_float_v1)                        \
     X(gpu_matmat_prob_prob_uniform_double_v1)                       \
+    X(cbcsr_matvec_transpose_heter_float)                           \
     X(gpu_matmat_prob_prob_normal_float_v1_ws)                      \
     X(gpu_matmat_prob_prob_normal_double_v1_ws)                     \
     X(gpu_matmat_prob_prob_uniform_float_v1_ws)                     \

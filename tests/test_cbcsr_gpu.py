@@ -114,3 +114,48 @@ def test_cbcsr_empty_and_errors(cuda):
     with pytest.raises(ValueError):
       bpl.csr_to_column_blocked(torch.zeros(0, device=cuda), torch.zeros(0, dtype=torch.int32, device=cuda),
                                 torch.as_tensor(indptr).to(cuda), shape=(5, 7), block_width=bad)
+
+
+@pytest.mark.parametrize('shape,density,width', [((3000, 2000), 0.02, 512), ((20000, 50000), 0.002, None),
+                                                 ((1, 40), 1.0, 32), ((700, 33000), 0.01, 32256)])
+def test_dense_vector_product_on_the_prepared_matrix(cuda, shape, density, width):
+  """csr_matvec(..., transpose=True, prepared=P): y = A^T x with a dense x, against the CPU oracle and the stateless
+  operator (float32 summation order differs: rtol 1e-5, atol 1e-5 * entries per column), zeros in x skipped, and the
+  vector's tangent / cotangent rules against dense algebra."""
+  import brainpylib_b200 as bpl
+  from oracle import cpu
+  data, indices, indptr, rng = cases.csr_case(shape, density, 31)
+  x = rng.uniform(-1, 1, shape[0]).astype(np.float32)
+  x[rng.random(shape[0]) < 0.3] = 0.0
+  d, ix, ptr, xv = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr, x))
+  prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=shape, block_width=width)
+  y = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=True, prepared=prepared)
+  want = cpu.csr_matvec(data, indices, indptr, x, shape=shape, transpose=True)
+  per_col = max(1.0, len(indices) / shape[1])
+  np.testing.assert_allclose(y.cpu().numpy(), want, rtol=1e-5, atol=1e-5 * per_col)
+  plain = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=True)
+  torch.testing.assert_close(y, plain, rtol=1e-5, atol=1e-5 * per_col)
+  if shape[0] * shape[1] <= 10_000_000:
+    dense = bpl.sparse_ops.csr_to_dense(d, ix, ptr, shape=shape)
+    xg = xv.clone().requires_grad_(True)
+    out = bpl.csr_matvec(d, ix, ptr, xg, shape=shape, transpose=True, prepared=prepared)
+    ct = torch.as_tensor(rng.standard_normal(shape[1]).astype(np.float32)).to(cuda)
+    out.backward(ct)
+    torch.testing.assert_close(xg.grad, dense @ ct, rtol=1e-4, atol=1e-4 * per_col)
+    t = torch.as_tensor(rng.standard_normal(shape[0]).astype(np.float32)).to(cuda)
+    _, tangent = torch.func.jvp(lambda v: bpl.csr_matvec(d, ix, ptr, v, shape=shape, transpose=True, prepared=prepared),
+                                (xv,), (t,))
+    torch.testing.assert_close(tangent, dense.T @ t, rtol=1e-4, atol=1e-4 * per_col)
+
+
+def test_dense_vector_product_refuses_fixed_point_and_wrong_operands(cuda):
+  import brainpylib_b200 as bpl
+  data, indices, indptr, rng = cases.csr_case((500, 400), 0.05, 3)
+  d, ix, ptr = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr))
+  x = torch.ones(500, device=cuda)
+  fixed = bpl.csr_to_column_blocked(d, ix, ptr, shape=(500, 400), block_width=128, accumulate='fixed')
+  with pytest.raises(ValueError, match='float'):
+    bpl.csr_matvec(d, ix, ptr, x, shape=(500, 400), transpose=True, prepared=fixed)
+  ok = bpl.csr_to_column_blocked(d, ix, ptr, shape=(500, 400), block_width=128)
+  with pytest.raises(ValueError, match='transpose=True'):
+    bpl.csr_matvec(d, ix, ptr, torch.ones(400, device=cuda), shape=(500, 400), transpose=False, prepared=ok)

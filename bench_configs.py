@@ -206,25 +206,26 @@ def bench_c2(args, device):
                                  'reference has no compiled CPU code for this operator and numba needs the reference tree)',
                        'us_per_call': sec * 1e6, 'host_cores_available': os.cpu_count()},
          reference_cuda=ref_entry)
-  # the transposed product on the matrix prepared once into the column-blocked layout (4 prepared copies rotate)
+  # both products on the matrix prepared once into the column-blocked layout (4 prepared copies rotate)
   prepared = [event_ops.csr_to_column_blocked(d, ix, base['indptr'], shape=c['shape']) for d, ix in copies]
-
-  def call_prepared(i):
-    sparse_ops.cbcsr_matvec_transpose_raw(prepared[i % 4], base['vector'], out=y)
-  us = time_graph(call_prepared, args.steps, args.warmup)
-  want = oracle_cpu.csr_matvec(c['data'], c['indices'], c['indptr'], c['vector'], shape=c['shape'], transpose=True)
-  call_prepared(0)
-  torch.cuda.synchronize()
-  err = float(np.abs(y.cpu().numpy() - want).max())
-  if not err < 1e-2:
-    raise SystemExit(f'c2 transpose=True on the prepared matrix: result differs from the CPU oracle by {err}')
-  nbytes = 6 * nnz + 8 * n * prepared[0].n_blocks + 4 * n + 4 * n + 4 * n
-  emit(config='c2 transpose=True, prepared matrix (csr_matvec(..., transpose=True, prepared=P))', transpose=True,
-       metric='synaptic_ops_per_sec', value=nnz / (us * 1e-6), unit='SyOp/s', us_per_call=us,
-       l2='4 rotating copies of the prepared matrix', max_abs_error_vs_cpu_oracle=err,
-       prepared_matrix={'bytes': prepared[0].nbytes(), 'block_width': prepared[0].block_width, 'n_blocks': prepared[0].n_blocks},
-       roofline={'bound': 'hbm', 'achieved': nbytes / (us * 1e-6) / 1e9, 'peak': peak, 'unit': 'GB/s',
-                 'frac': nbytes / (us * 1e-6) / 1e9 / peak, 'peak_source': src, 'algorithmic_bytes': nbytes})
+  for transpose in (False, True):
+    def call_prepared(i):
+      sparse_ops.cbcsr_matvec_raw(prepared[i % 4], base['vector'], transpose=transpose, out=y)
+    us = time_graph(call_prepared, args.steps, args.warmup)
+    want = oracle_cpu.csr_matvec(c['data'], c['indices'], c['indptr'], c['vector'], shape=c['shape'], transpose=transpose)
+    call_prepared(0)
+    torch.cuda.synchronize()
+    err = float(np.abs(y.cpu().numpy() - want).max())
+    if not err < 1e-2:
+      raise SystemExit(f'c2 transpose={transpose} on the prepared matrix: result differs from the CPU oracle by {err}')
+    nbytes = 6 * nnz + 8 * n * prepared[0].n_blocks + 4 * n + 4 * n + 4 * n
+    emit(config=f'c2 on the prepared matrix (csr_matvec(..., transpose={transpose}, prepared=P))', transpose=transpose,
+         metric='synaptic_ops_per_sec', value=nnz / (us * 1e-6), unit='SyOp/s', us_per_call=us,
+         l2='4 rotating copies of the prepared matrix', max_abs_error_vs_cpu_oracle=err,
+         prepared_matrix={'bytes': prepared[0].nbytes(), 'block_width': prepared[0].block_width,
+                          'n_blocks': prepared[0].n_blocks},
+         roofline={'bound': 'hbm', 'achieved': nbytes / (us * 1e-6) / 1e9, 'peak': peak, 'unit': 'GB/s',
+                   'frac': nbytes / (us * 1e-6) / 1e9 / peak, 'peak_source': src, 'algorithmic_bytes': nbytes})
   del prepared
   ev = torch.as_tensor(np.random.default_rng(1).random(n) < 0.05).to(device)
 

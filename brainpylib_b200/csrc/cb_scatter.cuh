@@ -129,6 +129,20 @@ __device__ __forceinline__ void cb_add_group_scaled(float *acc, const CbGroup &g
     cb_add_scaled(acc, g.cc.w >> 16, g.wb.w, s);
 }
 
+// gather direction: sum of weight * xs[column] over a group (xs: the block's slice of the vector in shared memory;
+// padding synapses have weight 0 and column 0)
+__device__ __forceinline__ float cb_dot_group(const float *xs, const CbGroup &g) {
+    float s = __uint_as_float(g.wa.x) * xs[g.cc.x & 0xffffu];
+    s = fmaf(__uint_as_float(g.wa.y), xs[g.cc.x >> 16], s);
+    s = fmaf(__uint_as_float(g.wa.z), xs[g.cc.y & 0xffffu], s);
+    s = fmaf(__uint_as_float(g.wa.w), xs[g.cc.y >> 16], s);
+    s = fmaf(__uint_as_float(g.wb.x), xs[g.cc.z & 0xffffu], s);
+    s = fmaf(__uint_as_float(g.wb.y), xs[g.cc.z >> 16], s);
+    s = fmaf(__uint_as_float(g.wb.z), xs[g.cc.w & 0xffffu], s);
+    s = fmaf(__uint_as_float(g.wb.w), xs[g.cc.w >> 16], s);
+    return s;
+}
+
 template<bool FIXED>
 __device__ __forceinline__ void cb_add_group(float *acc, const CbGroup &g) {
     cb_add<FIXED>(acc, g.cc.x & 0xffffu, g.wa.x);
@@ -205,7 +219,10 @@ __device__ __forceinline__ void cb_stamp(unsigned long long *trace, const uint32
 //   inv_scale: FIXED only, 2^-k.
 //   DENSE (with x): y = A^T x for a dense vector x instead of a spike list: every row whose x is not zero is walked and
 //   its weights are multiplied by x[row] (float accumulation only); counts / ids are not read, n_chunks = n_row.
-template<int NBUF, bool FIXED, int LOG_L, bool DENSE = false>
+//   GATHER (with DENSE): y = A x instead.  The shared-memory slice holds x[block] (not sums), every row is walked, a
+//   lane forms the dot product of its group with the slice, the team's lanes add up and one of them adds the sum to
+//   y[row] in global memory (y already zero; a row receives one addition per block and copy round).
+template<int NBUF, bool FIXED, int LOG_L, bool DENSE = false, bool GATHER = false>
 __device__ __forceinline__ void
 cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets, const uint32_t n_col,
                 const uint32_t width, const uint32_t n_blocks, const uint32_t b, const uint32_t p, const uint32_t P,
@@ -214,6 +231,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
                 unsigned char *smem, uint32_t *prefix, uint32_t *warp_total, const float inv_scale,
                 unsigned long long *trace = nullptr, const uint32_t trace_cta = 0, const float *__restrict__ x = nullptr) {
     static_assert(!(DENSE && FIXED), "the dense product accumulates in float");
+    static_assert(DENSE || !GATHER, "the gather direction is a dense-vector product");
     static_assert(NBUF <= 3, "the per-round scale registers cover three rounds in flight");
     constexpr uint32_t L = 1u << LOG_L, TEAMS = 32u / L;          // lanes (= slots) per team, teams per warp
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -229,7 +247,11 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
             trace[static_cast<uint64_t>(trace_cta) * 8u + 4] = 0ull;
         }
     }
-    for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = 0.0f;
+    if (GATHER) {
+        for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = x[col0 + j];
+    } else {
+        for (uint32_t j = threadIdx.x; j < my_width; j += CB_THREADS) acc[j] = 0.0f;
+    }
 
     uint32_t n_act;
     if (DENSE) {
@@ -251,12 +273,33 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
         if (k < K) {
             const uint32_t at = p + (warp + 32u * k) * P;
             const uint32_t row = DENSE ? at : list_row(prefix, n_chunks, chunk, ids, at);
-            if (DENSE) xs = x[row];
-            if (!DENSE || xs != 0.0f) {                          // a row whose vector entry is zero adds nothing
+            if (GATHER) xs = __uint_as_float(row);               // the row rides in the scale registers
+            else if (DENSE) xs = x[row];
+            if (!DENSE || GATHER || xs != 0.0f) {                // a row whose vector entry is zero adds nothing
                 const uint32_t *o = offsets + row * stride + b;
                 src = o[0];
                 rem = o[1] - src;
             }
+        }
+    };
+
+    // one round's buffer: scatter adds the lane's group into the slice; gather forms its dot product with the slice,
+    // sums over the team (whose slots hold consecutive groups of ONE row's segment) and adds to y[row]
+    auto consume = [&](const unsigned char *buf, const bool filled, const float tag) {
+        if (GATHER) {
+            float part = 0.0f;
+            if (filled) {
+                CbGroup grp;
+                grp.wa = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES);
+                grp.wb = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 16);
+                grp.cc = *reinterpret_cast<const uint4 *>(buf + lane * CB_GROUP_BYTES + 32);
+                part = cb_dot_group(acc, grp);
+            }
+#pragma unroll
+            for (uint32_t o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(FULL_MASK, part, o);
+            if (sub == 0 && filled) atomicAdd(y + __float_as_uint(tag), part);
+        } else {
+            cb_accumulate<FIXED, DENSE>(acc, buf, filled, lane, tag);
         }
     };
 
@@ -306,7 +349,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
             if (issued - consumed == NBUF) {                // ring full: accumulate the oldest round
                 cp_async_wait<NBUF - 1>();
                 __syncwarp();
-                cb_accumulate<FIXED, DENSE>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane, sc0);
+                consume(ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), sc0);
                 __syncwarp();
                 pieces >>= 8;
                 sc0 = sc1;
@@ -319,7 +362,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     cp_async_wait<0>();
     __syncwarp();
     while (consumed < issued) {
-        cb_accumulate<FIXED, DENSE>(acc, ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), lane, sc0);
+        consume(ring + (consumed % NBUF) * CB_BUF_BYTES, sub < (pieces & 0xffu), sc0);
         pieces >>= 8;
         sc0 = sc1;
         sc1 = sc2;
@@ -333,7 +376,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
     __syncthreads();
     if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 5);
     // flush the slice: coalesced vector reductions, P CTAs add into the same zero-filled y
-    if (mine > 0) {
+    if (mine > 0 && !GATHER) {
         float *out = y + col0;
         auto value = [&](const uint32_t j) -> float {
             return FIXED ? static_cast<float>(reinterpret_cast<const int *>(acc)[j]) * inv_scale : acc[j];

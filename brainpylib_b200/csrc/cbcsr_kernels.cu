@@ -53,7 +53,8 @@ event_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t
 }
 
 // y = A^T x for a dense float vector x on the same storage: every row with x[row] != 0 is walked, weights scaled by x[row].
-template<int NBUF, int LOG_L>
+// GATHER: y = A x instead: the block's slice of x sits in shared memory, a team sums a row's segment against it.
+template<int NBUF, int LOG_L, bool GATHER>
 __global__ void __launch_bounds__(CB_THREADS, 1)
 dense_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t *__restrict__ offsets,
                         const uint32_t n_row, const uint32_t n_col, const uint32_t width, const uint32_t n_blocks,
@@ -61,24 +62,25 @@ dense_cb_scatter_kernel(const unsigned char *__restrict__ groups, const uint32_t
     extern __shared__ __align__(128) unsigned char cb_smem[];
     __shared__ uint32_t prefix[2];            // unused by the dense walk
     __shared__ uint32_t warp_total[CB_WARPS];
-    cb_scatter_body<NBUF, false, LOG_L, true>(groups, offsets, n_col, width, n_blocks, blockIdx.x / P, blockIdx.x % P, P, 0,
-                                              n_row, nullptr, nullptr, y, acc_bytes, cb_smem, prefix, warp_total, 1.0f,
-                                              nullptr, 0, x);
+    cb_scatter_body<NBUF, false, LOG_L, true, GATHER>(groups, offsets, n_col, width, n_blocks, blockIdx.x / P,
+                                                      blockIdx.x % P, P, 0, n_row, nullptr, nullptr, y, acc_bytes, cb_smem,
+                                                      prefix, warp_total, 1.0f, nullptr, 0, x);
 }
 
 using CbDenseKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
                                const float *, float *, uint32_t);
-template<int NBUF>
+template<int NBUF, bool GATHER>
 CbDenseKernel cb_dense_kernel_for_lanes(uint32_t log_l) {
     switch (log_l) {
-        case 3: return dense_cb_scatter_kernel<NBUF, 3>;
-        case 4: return dense_cb_scatter_kernel<NBUF, 4>;
-        case 5: return dense_cb_scatter_kernel<NBUF, 5>;
-        default: return dense_cb_scatter_kernel<NBUF, 2>;
+        case 3: return dense_cb_scatter_kernel<NBUF, 3, GATHER>;
+        case 4: return dense_cb_scatter_kernel<NBUF, 4, GATHER>;
+        case 5: return dense_cb_scatter_kernel<NBUF, 5, GATHER>;
+        default: return dense_cb_scatter_kernel<NBUF, 2, GATHER>;
     }
 }
-CbDenseKernel cb_dense_kernel(uint32_t n_buf, uint32_t log_l) {
-    return n_buf == 3 ? cb_dense_kernel_for_lanes<3>(log_l) : cb_dense_kernel_for_lanes<2>(log_l);
+CbDenseKernel cb_dense_kernel(uint32_t n_buf, uint32_t log_l, bool gather) {
+    if (gather) return n_buf == 3 ? cb_dense_kernel_for_lanes<3, true>(log_l) : cb_dense_kernel_for_lanes<2, true>(log_l);
+    return n_buf == 3 ? cb_dense_kernel_for_lanes<3, false>(log_l) : cb_dense_kernel_for_lanes<2, false>(log_l);
 }
 
 using CbKernel = void (*)(const unsigned char *, const uint32_t *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t,
@@ -190,7 +192,8 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     launch_ok();
 }
 
-void cbcsr_matvec_transpose_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len) {
+// gather = false: y(n_col) = A^T x(n_row); gather = true: y(n_row) = A x(n_col)
+void cbcsr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len, const bool gather) {
     const CbDescriptor *d = unpack<CbDescriptor>(opaque, opaque_len);
     if (!d) return;
     const uint32_t n_row = d->n_row, n_col = d->n_col, width = d->block_width;
@@ -206,7 +209,11 @@ void cbcsr_matvec_transpose_impl(cudaStream_t stream, void **buffers, const char
         set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: team_lanes_log2 must be 2..5");
         return;
     }
-    if (n_col == 0) return;
+    if (n_col == 0) {
+        if (gather && n_row != 0 && cudaMemsetAsync(buffers[3], 0, sizeof(float) * static_cast<size_t>(n_row), stream) != cudaSuccess)
+            launch_ok();
+        return;
+    }
     const uint32_t n_blocks = (n_col + width - 1) / width;
     if (n_blocks > CB_MAX_BLOCKS) {
         set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: more than 1024 column blocks");
@@ -220,7 +227,8 @@ void cbcsr_matvec_transpose_impl(cudaStream_t stream, void **buffers, const char
         set_status(BPL_ERR_ARGUMENT, "column-blocked matrix: the group array must be 16-byte aligned");
         return;
     }
-    if (cudaMemsetAsync(y, 0, sizeof(float) * static_cast<size_t>(n_col), stream) != cudaSuccess) {
+    const size_t n_out = gather ? n_row : n_col;
+    if (n_out != 0 && cudaMemsetAsync(y, 0, sizeof(float) * n_out, stream) != cudaSuccess) {
         launch_ok();
         return;
     }
@@ -236,17 +244,19 @@ void cbcsr_matvec_transpose_impl(cudaStream_t stream, void **buffers, const char
     if (configured_device != dev) {
         for (uint32_t n_buf = 2; n_buf <= 3; ++n_buf)
             for (uint32_t log_l = 2; log_l <= 5; ++log_l)
-                if (cudaFuncSetAttribute(cb_dense_kernel(n_buf, log_l), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(CB_SMEM_LIMIT)) != cudaSuccess) {
-                    launch_ok();
-                    return;
-                }
+                for (int g = 0; g < 2; ++g)
+                    if (cudaFuncSetAttribute(cb_dense_kernel(n_buf, log_l, g != 0),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(CB_SMEM_LIMIT)) != cudaSuccess) {
+                        launch_ok();
+                        return;
+                    }
         configured_device = dev;
     }
     const uint32_t P = cb_shares(n_blocks);
     const uint32_t log_l = d->team_lanes_log2 == 0 ? 2u : d->team_lanes_log2;
     if (profile_before()) cudaEventRecord(profile_before(), stream);
-    cb_dense_kernel(plan.n_buf, log_l)<<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(
+    cb_dense_kernel(plan.n_buf, log_l, gather)<<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(
         groups, offsets, n_row, n_col, width, n_blocks, P, x, y, plan.acc_bytes);
     if (profile_after()) cudaEventRecord(profile_after(), stream);
     launch_ok();
@@ -263,7 +273,12 @@ extern "C" {
 // this product from cuSPARSE): buffers [groups, offsets, x f32(n_row), y f32(n_col)]; opaque as event_cbcsr_matvec_*
 // with fixed_point = 0.
 void cbcsr_matvec_transpose_heter_float(bpl_stream_t s, void **b, const char *o, size_t n) {
-    cbcsr_matvec_transpose_impl(s, b, o, n);
+    cbcsr_matvec_impl(s, b, o, n, false);
+}
+// y = A x on the same storage: buffers [groups, offsets, x f32(n_col), y f32(n_row)].  The block's slice of x is staged
+// in shared memory, so the gathers of x never leave the SM.
+void cbcsr_matvec_heter_float(bpl_stream_t s, void **b, const char *o, size_t n) {
+    cbcsr_matvec_impl(s, b, o, n, true);
 }
 
 void event_cbcsr_matvec_heter_float_bool(bpl_stream_t s, void **b, const char *o, size_t n) {

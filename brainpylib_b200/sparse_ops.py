@@ -113,56 +113,58 @@ class _CSRMatvec(torch.autograd.Function):
     return loop_vmap(_CSRMatvec.apply, info, in_dims, (data, indices, indptr, vector, shape, transpose, method))
 
 
-def cbcsr_matvec_transpose_raw(prepared, vector, *, out=None):
-  """``y = A^T x`` on a matrix converted once with ``event_ops.csr_to_column_blocked`` (float accumulation); target
-  ``cbcsr_matvec_transpose_heter_float``.  No counterpart in the reference."""
+def cbcsr_matvec_raw(prepared, vector, *, transpose, out=None):
+  """``y = A^T x`` (``transpose``) or ``y = A x`` on a matrix converted once with ``event_ops.csr_to_column_blocked``
+  (float accumulation); targets ``cbcsr_matvec_transpose_heter_float`` / ``cbcsr_matvec_heter_float``.  No counterpart
+  in the reference."""
   from . import event_ops
   n_row, n_col = prepared.shape
+  n_in, n_out = (n_row, n_col) if transpose else (n_col, n_row)
   if prepared.scale_log2 is not None:
     raise ValueError('the dense-vector product needs a matrix prepared with accumulate=\'float\'')
-  if vector.dtype != torch.float32 or vector.shape != (n_row,):
-    raise ValueError(f'vector must be float32 of shape ({n_row},)')
+  if vector.dtype != torch.float32 or vector.shape != (n_in,):
+    raise ValueError(f'vector must be float32 of shape ({n_in},)')
   opaque = event_ops._cb_descriptor(n_row, n_col, prepared.block_width, None, prepared.team_lanes_log2)
   if out is None:
-    out = torch.empty(n_col, dtype=torch.float32, device=vector.device)
-  _lib.call('cbcsr_matvec_transpose_heter_float', [prepared.groups, prepared.offsets, vector, out], opaque,
-            device=vector.device)
+    out = torch.empty(n_out, dtype=torch.float32, device=vector.device)
+  name = 'cbcsr_matvec_transpose_heter_float' if transpose else 'cbcsr_matvec_heter_float'
+  _lib.call(name, [prepared.groups, prepared.offsets, vector, out], opaque, device=vector.device)
   return out
 
 
+def cbcsr_matvec_transpose_raw(prepared, vector, *, out=None):
+  return cbcsr_matvec_raw(prepared, vector, transpose=True, out=out)
+
+
 class _CSRMatvecPrepared(torch.autograd.Function):
-  """``y = A^T x`` on the prepared matrix.  Linear in ``x``: reverse mode is ``A ct`` on the CSR arrays, forward mode
-  the same product on the tangent; the prepared weights are constants (no gradient w.r.t. ``data``)."""
+  """The dense-vector product on the prepared matrix, either orientation.  Linear in ``x``: reverse mode is the other
+  orientation on the same prepared matrix, forward mode the same product on the tangent; the prepared weights are
+  constants (no gradient w.r.t. ``data``)."""
 
   @staticmethod
-  def forward(data, indices, indptr, vector, shape, prepared):
-    return cbcsr_matvec_transpose_raw(prepared, vector)
+  def forward(vector, prepared, transpose):
+    return cbcsr_matvec_raw(prepared, vector, transpose=transpose)
 
   @staticmethod
   def setup_context(ctx, inputs, output):
-    data, indices, indptr, _vector, shape, prepared = inputs
-    ctx.save_for_backward(data, indices, indptr)
-    ctx.save_for_forward(data, indices, indptr)
-    ctx.shape, ctx.prepared = shape, prepared
+    _vector, ctx.prepared, ctx.transpose = inputs
 
   @staticmethod
   def backward(ctx, ct):
-    data, indices, indptr = ctx.saved_tensors
     g_vec = None
-    if ctx.needs_input_grad[3]:
-      g_vec = _CSRMatvec.apply(data, indices, indptr, contiguous(ct), ctx.shape, False, 'vector')
-    return None, None, None, g_vec, None, None
+    if ctx.needs_input_grad[0]:
+      g_vec = _CSRMatvecPrepared.apply(contiguous(ct), ctx.prepared, not ctx.transpose)
+    return g_vec, None, None
 
   @staticmethod
-  def jvp(ctx, _data_dot, _indices, _indptr, vector_dot, _shape, _prepared):
+  def jvp(ctx, vector_dot, _prepared, _transpose):
     if vector_dot is None:
       return None
-    data, indices, indptr = ctx.saved_tensors
-    return _CSRMatvecPrepared.apply(data, indices, indptr, contiguous(vector_dot), ctx.shape, ctx.prepared)
+    return _CSRMatvecPrepared.apply(contiguous(vector_dot), ctx.prepared, ctx.transpose)
 
   @staticmethod
-  def vmap(info, in_dims, data, indices, indptr, vector, shape, prepared):
-    return loop_vmap(_CSRMatvecPrepared.apply, info, in_dims, (data, indices, indptr, vector, shape, prepared))
+  def vmap(info, in_dims, vector, prepared, transpose):
+    return loop_vmap(_CSRMatvecPrepared.apply, info, in_dims, (vector, prepared, transpose))
 
 
 def _prepare(data, indices, indptr, vector):
@@ -212,10 +214,11 @@ def csr_matvec(
   transpose: bool
     Whether to transpose the sparse matrix before computing.
   prepared: ColumnBlockedCSR, optional
-    Not in the reference.  With ``transpose=True`` and float32 heterogeneous weights: the same matrix converted once
-    with ``event_ops.csr_to_column_blocked`` (float accumulation); the product then accumulates in shared memory
-    instead of through one L2 reduction per stored entry.  Same result up to the order of float32 additions; the
-    weights inside ``prepared`` are constants for differentiation.
+    Not in the reference.  For float32 heterogeneous weights: the same matrix converted once with
+    ``event_ops.csr_to_column_blocked`` (float accumulation).  ``transpose=True`` then accumulates in shared memory
+    instead of through one L2 reduction per stored entry, ``transpose=False`` gathers the vector from shared memory
+    instead of through L1 / L2.  Same result up to the order of float32 additions; the weights inside ``prepared``
+    are constants for differentiation.
 
   Returns
   -------
@@ -237,13 +240,11 @@ def csr_matvec(
   if vector.shape[0] != (shape[0] if transpose else shape[1]):
     raise ValueError(f'shape {shape} does not match the given vector {tuple(vector.shape)}.')
   if prepared is not None:
-    if not transpose or data.dtype != torch.float32 or data.shape[0] == 1:
-      raise ValueError('prepared= applies to transpose=True with float32 heterogeneous weights')
+    if data.dtype != torch.float32 or data.shape[0] == 1:
+      raise ValueError('prepared= applies to float32 heterogeneous weights')
     if tuple(prepared.shape) != (int(shape[0]), int(shape[1])):
       raise ValueError(f'the prepared matrix has shape {prepared.shape}, not {tuple(shape)}')
-    data, indices, indptr, vector = map(contiguous, (data, indices, indptr, vector))
-    return _CSRMatvecPrepared.apply(data, indices.to(torch.int32), indptr.to(torch.int32), vector,
-                                    (int(shape[0]), int(shape[1])), prepared)
+    return _CSRMatvecPrepared.apply(contiguous(vector), prepared, bool(transpose))
   return _dispatch(data, indices, indptr, vector, shape, transpose, method)
 
 

@@ -122,6 +122,10 @@ void bpl_profile_scatter_events(void *before, void *after);
  *   y = A^T x for a dense float32 vector x on the same storage: every row with x[row] != 0 is walked and its weights
  *   are multiplied by x[row]; float accumulation (fixed_point must be 0).
  *   buffers [groups, offsets, x f32(n_row), y f32(n_col)]; opaque as above
+ * cbcsr_matvec_heter_float             (no counterpart in the reference)
+ *   y = A x on the same storage: a block's slice of x is staged in shared memory and a row's segment is summed against
+ *   it, so the gathers of x never leave the SM; a row receives one global addition per column block and copy round.
+ *   buffers [groups, offsets, x f32(n_col), y f32(n_row)]; opaque as above
  *
  * event_cbcsr_matvec_list_heter_float / event_csr_matvec_list_heter_float   (no counterpart in the reference)
  *   the scatter half alone, driven by a ready-made spike list (counts[1024], then row ids in chunk segments: the
@@ -247,7 +251,7 @@ void bpl_profile_scatter_events(void *before, void *after);
     X(gpu_matmat_prob_prob_normal_double_v3)                        \
     X(gpu_matmat_prob_prob_uniform_float_v1)                        \
     X(gpu_matmat_prob_prob_uniform_double_v1)                       \
-    X(cbcsr_matvec_transpose_heter_float)                           \
+    X(cbcsr_matvec_transpose_heter_float) X(cbcsr_matvec_heter_float) \
     X(gpu_matmat_prob_prob_normal_float_v1_ws)                      \
     X(gpu_matmat_prob_prob_normal_double_v1_ws)                     \
     X(gpu_matmat_prob_prob_uniform_float_v1_ws)                     \

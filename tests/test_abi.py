@@ -38,7 +38,7 @@ def test_library_exports_every_declared_symbol():
 def test_registrations_are_xla_capsules():
   from brainpylib_b200 import gpu_ops
   regs = gpu_ops.registrations()
-  assert len(regs) == len(gpu_ops.target_names()) == 128
+  assert len(regs) == len(gpu_ops.target_names()) == 129
   get_name = ctypes.pythonapi.PyCapsule_GetName
   get_name.restype = ctypes.c_char_p
   get_name.argtypes = [ctypes.py_object]

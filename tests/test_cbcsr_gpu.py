@@ -116,36 +116,39 @@ def test_cbcsr_empty_and_errors(cuda):
                                 torch.as_tensor(indptr).to(cuda), shape=(5, 7), block_width=bad)
 
 
+@pytest.mark.parametrize('transpose', [True, False])
 @pytest.mark.parametrize('shape,density,width', [((3000, 2000), 0.02, 512), ((20000, 50000), 0.002, None),
                                                  ((1, 40), 1.0, 32), ((700, 33000), 0.01, 32256)])
-def test_dense_vector_product_on_the_prepared_matrix(cuda, shape, density, width):
-  """csr_matvec(..., transpose=True, prepared=P): y = A^T x with a dense x, against the CPU oracle and the stateless
-  operator (float32 summation order differs: rtol 1e-5, atol 1e-5 * entries per column), zeros in x skipped, and the
+def test_dense_vector_product_on_the_prepared_matrix(cuda, shape, density, width, transpose):
+  """csr_matvec(..., prepared=P) in both orientations with a dense x, against the CPU oracle and the stateless
+  operator (float32 summation order differs: rtol 1e-5, atol 1e-5 * entries per output), zeros in x skipped, and the
   vector's tangent / cotangent rules against dense algebra."""
   import brainpylib_b200 as bpl
   from oracle import cpu
   data, indices, indptr, rng = cases.csr_case(shape, density, 31)
-  x = rng.uniform(-1, 1, shape[0]).astype(np.float32)
-  x[rng.random(shape[0]) < 0.3] = 0.0
+  n_in, n_out = (shape[0], shape[1]) if transpose else (shape[1], shape[0])
+  x = rng.uniform(-1, 1, n_in).astype(np.float32)
+  x[rng.random(n_in) < 0.3] = 0.0
   d, ix, ptr, xv = (torch.as_tensor(a).to(cuda) for a in (data, indices, indptr, x))
   prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=shape, block_width=width)
-  y = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=True, prepared=prepared)
-  want = cpu.csr_matvec(data, indices, indptr, x, shape=shape, transpose=True)
-  per_col = max(1.0, len(indices) / shape[1])
-  np.testing.assert_allclose(y.cpu().numpy(), want, rtol=1e-5, atol=1e-5 * per_col)
-  plain = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=True)
-  torch.testing.assert_close(y, plain, rtol=1e-5, atol=1e-5 * per_col)
+  y = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=transpose, prepared=prepared)
+  want = cpu.csr_matvec(data, indices, indptr, x, shape=shape, transpose=transpose)
+  per_out = max(1.0, len(indices) / n_out)
+  np.testing.assert_allclose(y.cpu().numpy(), want, rtol=1e-5, atol=1e-5 * per_out)
+  plain = bpl.csr_matvec(d, ix, ptr, xv, shape=shape, transpose=transpose)
+  torch.testing.assert_close(y, plain, rtol=1e-5, atol=1e-5 * per_out)
   if shape[0] * shape[1] <= 10_000_000:
     dense = bpl.sparse_ops.csr_to_dense(d, ix, ptr, shape=shape)
+    op = dense.T if transpose else dense
     xg = xv.clone().requires_grad_(True)
-    out = bpl.csr_matvec(d, ix, ptr, xg, shape=shape, transpose=True, prepared=prepared)
-    ct = torch.as_tensor(rng.standard_normal(shape[1]).astype(np.float32)).to(cuda)
+    out = bpl.csr_matvec(d, ix, ptr, xg, shape=shape, transpose=transpose, prepared=prepared)
+    ct = torch.as_tensor(rng.standard_normal(n_out).astype(np.float32)).to(cuda)
     out.backward(ct)
-    torch.testing.assert_close(xg.grad, dense @ ct, rtol=1e-4, atol=1e-4 * per_col)
-    t = torch.as_tensor(rng.standard_normal(shape[0]).astype(np.float32)).to(cuda)
-    _, tangent = torch.func.jvp(lambda v: bpl.csr_matvec(d, ix, ptr, v, shape=shape, transpose=True, prepared=prepared),
+    torch.testing.assert_close(xg.grad, op.T @ ct, rtol=1e-4, atol=1e-4 * per_out)
+    t = torch.as_tensor(rng.standard_normal(n_in).astype(np.float32)).to(cuda)
+    _, tangent = torch.func.jvp(lambda v: bpl.csr_matvec(d, ix, ptr, v, shape=shape, transpose=transpose, prepared=prepared),
                                 (xv,), (t,))
-    torch.testing.assert_close(tangent, dense.T @ t, rtol=1e-4, atol=1e-4 * per_col)
+    torch.testing.assert_close(tangent, op @ t, rtol=1e-4, atol=1e-4 * per_out)
 
 
 def test_dense_vector_product_refuses_fixed_point_and_wrong_operands(cuda):
@@ -156,6 +159,7 @@ def test_dense_vector_product_refuses_fixed_point_and_wrong_operands(cuda):
   fixed = bpl.csr_to_column_blocked(d, ix, ptr, shape=(500, 400), block_width=128, accumulate='fixed')
   with pytest.raises(ValueError, match='float'):
     bpl.csr_matvec(d, ix, ptr, x, shape=(500, 400), transpose=True, prepared=fixed)
-  ok = bpl.csr_to_column_blocked(d, ix, ptr, shape=(500, 400), block_width=128)
-  with pytest.raises(ValueError, match='transpose=True'):
-    bpl.csr_matvec(d, ix, ptr, torch.ones(400, device=cuda), shape=(500, 400), transpose=False, prepared=ok)
+  other = bpl.csr_to_column_blocked(d, ix, ptr, shape=(500, 400), block_width=128)
+  other.shape = (500, 401)
+  with pytest.raises(ValueError, match='prepared matrix has shape'):
+    bpl.csr_matvec(d, ix, ptr, x, shape=(500, 400), transpose=True, prepared=other)

@@ -258,6 +258,7 @@ cb_scatter_body(const unsigned char *__restrict__ groups, const uint32_t *__rest
         n_act = n_chunks;
         __syncthreads();                                                             // the slice is zero
     } else {
+        pdl_wait();                                                                  // the spike list (and the zeroed y) are ready
         n_act = cb_chunk_prefix(counts, n_chunks, prefix, warp_total);               // ends with a barrier
     }
     if (threadIdx.x == 0) cb_stamp(trace, trace_cta, 1);

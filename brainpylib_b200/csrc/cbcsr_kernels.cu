@@ -185,9 +185,12 @@ void event_cbcsr_impl(cudaStream_t stream, void **buffers, const char *opaque, s
     }
     const uint32_t log_l = d->team_lanes_log2 == 0 ? 2u : d->team_lanes_log2;
     if (profile_before()) cudaEventRecord(profile_before(), stream);
-    cb_kernel(plan.n_buf, d->fixed_point != 0, log_l)<<<n_blocks * P, CB_THREADS, plan.smem_bytes, stream>>>(
-        groups, offsets, n_col, width, n_blocks, P, p.chunk, p.n_chunks, counts, ids, y, plan.acc_bytes, inv_scale,
-        g_cb_trace);
+    // behind the scan of this call the scatter is a dependent launch: it clears its slice while the scan still runs
+    const cudaError_t e = launch_dependent(cb_kernel(plan.n_buf, d->fixed_point != 0, log_l), dim3(n_blocks * P),
+                                           dim3(CB_THREADS), plan.smem_bytes, stream, groups, offsets, n_col, width,
+                                           n_blocks, P, p.chunk, p.n_chunks, counts, ids, y, plan.acc_bytes, inv_scale,
+                                           g_cb_trace);
+    if (e != cudaSuccess) set_status(BPL_ERR_CUDA, cudaGetErrorString(e));
     if (profile_after()) cudaEventRecord(profile_after(), stream);
     launch_ok();
 }

@@ -29,6 +29,31 @@ __device__ __forceinline__ uint2 ldg_stream_u2(const void *p) {
     return v;
 }
 
+// Programmatic dependent launch (scan -> scatter pairs): the scan lets its dependents start as soon as it runs, the
+// scatter does everything that needs no input from the scan (clearing its shared memory) and then waits here until
+// the scan has completed and its writes are visible.  In a kernel that was launched the ordinary way the wait returns
+// at once.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch of a kernel that may start before the kernel in front of it on the stream has finished (it must call
+// pdl_wait() before it touches anything that kernel writes).
+template<typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Reduction without a return value (one L2 operation, nothing travels back), spelled out so that no
 // call site can turn into the value-returning form.
 __device__ __forceinline__ void red_add(float *p, float v) {

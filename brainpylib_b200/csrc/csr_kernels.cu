@@ -179,12 +179,14 @@ void event_csr_matvec_impl(cudaStream_t stream, void **buffers, const char *opaq
         // one warp per work item; the grid is sized for the worst case (every row active) but capped
         const int grid = persistent_blocks(4, static_cast<uint64_t>(n_row) * 16);
         if (profile_before()) cudaEventRecord(profile_before(), stream);
-        if (vec)
-            row_scatter_kernel<T, HOMO, true, true><<<grid, ROW_THREADS, 0, stream>>>(
-                indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
-        else
-            row_scatter_kernel<T, HOMO, true, false><<<grid, ROW_THREADS, 0, stream>>>(
-                indices, indptr, data, nullptr, n_row, p.chunk, p.n_chunks, counts, ids, y);
+        // a dependent launch behind the scan: the blocks are resident and wait only where they first read the list
+        const cudaError_t e =
+            vec ? launch_dependent(row_scatter_kernel<T, HOMO, true, true>, dim3(grid), dim3(ROW_THREADS), 0, stream, indices,
+                                   indptr, data, static_cast<const T *>(nullptr), n_row, p.chunk, p.n_chunks, counts, ids, y)
+                : launch_dependent(row_scatter_kernel<T, HOMO, true, false>, dim3(grid), dim3(ROW_THREADS), 0, stream,
+                                   indices, indptr, data, static_cast<const T *>(nullptr), n_row, p.chunk, p.n_chunks, counts,
+                                   ids, y);
+        if (e != cudaSuccess) set_status(BPL_ERR_CUDA, cudaGetErrorString(e));
         if (profile_after()) cudaEventRecord(profile_after(), stream);
         launch_ok();
     } else {

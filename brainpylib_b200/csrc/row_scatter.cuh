@@ -122,7 +122,10 @@ row_scatter_body(const uint32_t *__restrict__ indices, const uint32_t *__restric
                  const uint32_t block_index, const uint32_t block_count /* the blocks that share the work */) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t n_list = n_row;
-    if (LIST) n_list = chunk_prefix(counts, n_chunks, prefix, warp_total);
+    if (LIST) {
+        pdl_wait();                                    // the spike list (and the zeroed y) are ready
+        n_list = chunk_prefix(counts, n_chunks, prefix, warp_total);
+    }
     if (n_list == 0) return;
 
     const uint32_t nse = indptr[n_row];

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 scan_events_kernel(const E *__restrict__ events, const uint32_t n_row, const uint32_t chunk,
                    const uint32_t n_chunks, T *__restrict__ y, const uint32_t n_out,
                    uint32_t *__restrict__ counts, uint32_t *__restrict__ ids) {
+    pdl_launch_dependents();   // the scatter behind this kernel may set itself up now; it waits before reading the list
     // (1) zero-fill the output (the reference does it with a cudaMemset on the wrong stream,
     //     lib/gpu_event_csr_matvec.cu:170).
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * SCAN_THREADS + threadIdx.x; i < n_out;

@@ -88,3 +88,26 @@ def test_sharded_host_steps_on_one_rank(cuda, dtype, accumulate, group):
       want = bpl.event_csr_matvec(d, ix, ptr, ev[s].to(cuda), shape=shape, transpose=True, prepared=prepared)
       torch.testing.assert_close(out[s].to(cuda), want, rtol=1e-5, atol=1e-5)
     out.fill_(float('nan'))
+
+
+@pytest.mark.parametrize('steps', [1, 2, 3, 4, 7])
+def test_runs_shorter_than_a_group_and_ragged_last_groups(cuda, steps):
+  """Runs of fewer steps than one group, exactly one group, and a ragged last group, single-device and sharded."""
+  import brainpylib_b200 as bpl
+  from brainpylib_b200 import sharded
+  shape = (12000, 5000)
+  (d, ix, ptr), rng = _case(shape, 0.004, 47, cuda)
+  prepared = bpl.csr_to_column_blocked(d, ix, ptr, shape=shape, block_width=1024)
+  ev = torch.from_numpy(rng.random((steps, shape[0])) < 0.03).float().pin_memory()
+  want = [bpl.event_csr_matvec(d, ix, ptr, ev[s].to(cuda), shape=shape, transpose=True, prepared=prepared)
+          for s in range(steps)]
+  out = torch.full((steps, shape[1]), float('nan')).pin_memory()
+  bpl.HostSteps(prepared, shape=shape, group=3).run(ev, out)
+  for s in range(steps):
+    torch.testing.assert_close(out[s].to(cuda), want[s], rtol=1e-5, atol=1e-5)
+  out.fill_(float('nan'))
+  ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=100000)
+  ex.run_host_steps(prepared, ev, out, group=3)
+  ex.check()
+  for s in range(steps):
+    torch.testing.assert_close(out[s].to(cuda), want[s], rtol=1e-5, atol=1e-5)

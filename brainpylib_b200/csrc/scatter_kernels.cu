@@ -70,11 +70,30 @@ __global__ void __launch_bounds__(THREADS)
 coo_atomic_kernel(const uint32_t size, const T *__restrict__ values, const I *__restrict__ pre_ids,
                   const I *__restrict__ post_ids, T *__restrict__ y) {
     const T w0 = values[0];
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * THREADS + threadIdx.x; i < size;
-         i += static_cast<uint64_t>(gridDim.x) * THREADS) {
-        const T v = HOMO ? w0 : values[pre_ids[i]];
-        if (PROD) atomic_mul(y + post_ids[i], v);
-        else atomicAdd(y + post_ids[i], v);
+    // a block takes 4 * THREADS consecutive entries, four per thread: the id loads, then the gathers of `values`, then
+    // the reductions, so that four dependent chains (id -> value -> reduction) are in flight instead of one.  One
+    // block per tile, not a persistent grid: with many more blocks than the SMs hold the L2 reductions spread better
+    // (a persistent grid of 8 blocks per SM measured 73-75 us for 1e7 entries, this form the reduction floor).
+    const uint64_t i0 = static_cast<uint64_t>(blockIdx.x) * (4 * THREADS) + threadIdx.x;
+    I pre[4], post[4];
+    T v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const uint64_t i = i0 + u * THREADS;
+        if (i < size) {
+            post[u] = post_ids[i];
+            if (!HOMO) pre[u] = pre_ids[i];
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        if (i0 + u * THREADS < size) v[u] = HOMO ? w0 : values[pre[u]];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if (i0 + u * THREADS < size) {
+            if (PROD) atomic_mul(y + post[u], v[u]);
+            else red_add(y + post[u], v[u]);
+        }
     }
 }
 
@@ -131,7 +150,12 @@ void coo_atomic_impl(cudaStream_t stream, void **buffers, const char *opaque, si
     const I *post_ids = static_cast<const I *>(buffers[HOMO ? 1 : 2]);
     T *y = static_cast<T *>(buffers[HOMO ? 2 : 3]);
     if (!fill<T>(stream, y, post_size, PROD ? T(1) : T(0)) || conn_size == 0) return;
-    coo_atomic_kernel<T, I, HOMO, PROD><<<grid_for(conn_size), THREADS, 0, stream>>>(
+    const uint64_t tiles = (static_cast<uint64_t>(conn_size) + 4 * THREADS - 1) / (4 * THREADS);
+    if (tiles > 0x7fffffffull) {
+        set_status(BPL_ERR_ARGUMENT, "coo_atomic: too many entries for one launch");
+        return;
+    }
+    coo_atomic_kernel<T, I, HOMO, PROD><<<static_cast<unsigned int>(tiles), THREADS, 0, stream>>>(
         conn_size, values, pre_ids, post_ids, y);
     launch_ok();
 }

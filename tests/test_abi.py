@@ -213,3 +213,58 @@ def test_sharded_step_refuses_bad_arguments_before_any_launch():
   code, text = step(slots=4)
   assert code == 3 and 'null' in text
   lib.bpl_clear_status()
+
+
+def test_host_step_runs_refuse_bad_arguments_before_any_launch():
+  """bpl_run_host_steps / bpl_sharded_run_host_steps check their arguments on the host: unknown target, group outside
+  1..16, missing ring buffers, streams that are not distinct."""
+  from brainpylib_b200 import _lib
+  lib = _lib.lib()
+  vp, u32, i32, sz = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int, ctypes.c_size_t
+  run = lib.bpl_run_host_steps
+  run.restype = None
+  run.argtypes = [ctypes.c_char_p, ctypes.c_char_p, sz, vp, i32, i32, i32, i32, vp, vp, vp, u32, vp, sz, vp, sz, u32, u32,
+                  vp, vp, vp]
+  msg = ctypes.create_string_buffer(256)
+  opaque = b'\0' * 12
+  bufs = (vp * 6)(*[0x1000 + 256 * i for i in range(6)])          # never dereferenced by the checks
+  ring3 = (vp * 3)(0x9000, 0xa000, 0xb000)
+  host = ctypes.create_string_buffer(64)
+
+  def call(name=b'event_csr_matvec_heter_float_float', group=1, in_ring=ring3, streams=(0x10, 0x20, 0x30), n_buffers=6):
+    lib.bpl_clear_status()
+    run(name, opaque, 12, bufs, n_buffers, 3, 4, 5, in_ring, ring3, ring3, group, ctypes.cast(host, vp), 16,
+        ctypes.cast(host, vp), 16, 1, 4, *streams)
+    return lib.bpl_last_status(msg, 256), msg.value.decode()
+
+  assert call(name=b'no_such_target') == (3, 'host steps: unknown target')
+  code, text = call(group=0)
+  assert code == 3 and 'group' in text
+  code, text = call(group=17)
+  assert code == 3 and 'group' in text
+  code, text = call(in_ring=(vp * 3)(0x9000, None, 0xb000))
+  assert code == 3 and 'null buffer' in text
+  code, text = call(streams=(0x10, 0x10, 0x30))
+  assert code == 3 and 'distinct' in text
+  code, text = call(n_buffers=3)
+  assert code == 3 and 'out of range' in text
+
+  srun = lib.bpl_sharded_run_host_steps
+  srun.restype = None
+  srun.argtypes = [vp, vp, u32, u32, i32, i32, u32, i32, u32, u32, vp, sz, vp, vp, i32, i32, i32, u32, vp, vp, u32, vp, vp,
+                   u32, u32, vp, vp, vp]
+  ring4 = (vp * 4)(0x9000, 0xa000, 0xb000, 0xc000)
+
+  def scall(group=1, ev_ring=ring4, streams=(0x10, 0x20, 0x30)):
+    lib.bpl_clear_status()
+    srun(0x1000, 0x2000, 10, 32, 0, 0, 2, 1, 10, 0, None, 1024, None, None, 1, 0, 4, 10, ev_ring, ring3, group,
+         ctypes.cast(host, vp), ctypes.cast(host, vp), 1, 4, *streams)
+    return lib.bpl_last_status(msg, 256), msg.value.decode()
+
+  code, text = scall(group=0)
+  assert code == 3 and 'group' in text
+  code, text = scall(ev_ring=(vp * 4)(0x9000, 0xa000, 0xb000, None))      # the buffer of step 0 is missing
+  assert code == 3 and 'null buffer' in text
+  code, text = scall(streams=(0x10, 0x20, 0x20))
+  assert code == 3 and 'distinct' in text
+  lib.bpl_clear_status()

@@ -20,7 +20,8 @@ reference's exact signature), `prepared_fixed_point` the prepared matrix with fi
 `roofline` is for the dominant kernel of `value` alone (CUDA events recorded around it by the library's
 profiling hook).  `e2e` drives the C-ABI target with HOST buffers (`HostSteps`, `bpl_run_host_steps`): every step
 copies that step's spikes from pinned host memory and the result back, three streams, enqueued by native code.
-N > 1 GPUs.  The matrix is sharded by post-synaptic neuron (each shard prepared like the 1-GPU matrix), every rank owns 1/N of the
+N > 1 GPUs.  The matrix is sharded by post-synaptic neuron (shards prepared like the 1-GPU matrix while a rank keeps
+>= 200,000 columns, plain CSR below: sharded.preferred_layout), every rank owns 1/N of the
 spike sources, one launch per step pushes the next step's spike list to the peers and scatters this
 step's; `e2e` moves only the rank's own n/N spikes in and its own slice of the result out.
 `cpu_baseline` / `--impl reference` time the reference's own CPU kernel (lib/cpu_event_sum.cc compiled
@@ -713,30 +714,39 @@ def run_sharded(args, torch, dist, device, world):
       raise SystemExit(f'sharded step ({layout}): the result of the last step differs from the stand-alone operator')
     return t.item()
 
+  layout = sharded.preferred_layout(shape[1])        # the storage of the shard the library recommends at this size
+  other = 'csr' if layout == 'prepared' else 'prepared'
+  shard = {'prepared': prepared, 'csr': (work['data'], work['indices'], work['indptr'])}
   with sampler:
-    ms_csr = timed_run('csr')
-    ms = timed_run('prepared')
-    # the scatter of this rank's shard alone (stand-alone operator on the assembled vector), for the roofline
+    ms_by_layout = {'csr': timed_run('csr'), 'prepared': timed_run('prepared')}
+    ms = ms_by_layout[layout]
+    # the scatter of this rank's shard alone (stand-alone operators on the assembled vector), for the roofline
     name = 'event_csr_matvec_heter_float_float'
     opaque = gpu_ops.build_twouint_onebool_descriptor(shape[0], shape[1], True)
     ws = torch.empty(_lib.workspace_bytes(name, opaque), dtype=torch.uint8, device=device)
     ev_rot = [torch.from_numpy(ev_all[W + i]).to(device) for i in range(min(K, 8))]
     y_tmp = torch.empty(shape[1], dtype=torch.float32, device=device)
-    k_ms_csr = kernel_time_ms(torch, lib, lambda s: event_ops.event_csr_matvec_raw(
-      work['data'], work['indices'], work['indptr'], ev_rot[s % len(ev_rot)], shape=shape, transpose=True, out=y_tmp,
-      workspace=ws), 0, min(K, 16))
     cb_name = 'event_cbcsr_matvec_heter_float_float'
     cb_opaque = event_ops._cb_descriptor(shape[0], shape[1], prepared.block_width, prepared.scale_log2,
                                          prepared.team_lanes_log2)
     cb_ws = torch.empty(_lib.workspace_bytes(cb_name, cb_opaque), dtype=torch.uint8, device=device)
-    k_ms = kernel_time_ms(torch, lib, lambda s: event_ops.event_cbcsr_matvec_raw(
-      prepared, ev_rot[s % len(ev_rot)], out=y_tmp, workspace=cb_ws), 0, min(K, 16))
+    k_ms_by_layout = {
+      'csr': kernel_time_ms(torch, lib, lambda s: event_ops.event_csr_matvec_raw(
+        work['data'], work['indices'], work['indptr'], ev_rot[s % len(ev_rot)], shape=shape, transpose=True, out=y_tmp,
+        workspace=ws), 0, min(K, 16)),
+      'prepared': kernel_time_ms(torch, lib, lambda s: event_ops.event_cbcsr_matvec_raw(
+        prepared, ev_rot[s % len(ev_rot)], out=y_tmp, workspace=cb_ws), 0, min(K, 16))}
     # ---- e2e: own spikes in, own slice of the result out, every step, through the exchange ----
-    e2e = run_e2e_sharded(torch, dist, prepared, exchange, ev_host_mine, shape, W, K, device, want)
+    e2e = run_e2e_sharded(torch, dist, shard[layout], exchange, ev_host_mine, shape, W, K, device, want)
   n_act = float(np.mean([o / DEGREE for o in ops_per_step[W:W + K]]))
   s_local = float(work['indices'].numel()) / (n_neurons * DEGREE) * n_act * DEGREE   # this rank's synapses per step
-  k_bytes = 6.0 * s_local + 8.0 * n_act * prepared.n_blocks + 4.0 * shape[1]
-  k_bytes_csr = 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]
+  k_bytes_by_layout = {'prepared': 6.0 * s_local + 8.0 * n_act * prepared.n_blocks + 4.0 * shape[1],
+                       'csr': 8.0 * s_local + 8.0 * n_act + 4.0 * shape[1]}
+  kernel_name = {'prepared': 'event_cb_scatter_kernel on one rank\'s prepared shard (stand-alone)',
+                 'csr': 'row_scatter_kernel<float, heter, list, vec> on one rank\'s CSR shard (stand-alone)'}
+  traffic_ratio = {'prepared': 1.14, 'csr': 1.046}
+  step_call = {'prepared': 'bpl_sharded_cb_step', 'csr': 'bpl_sharded_step'}
+  k_bytes, k_ms = k_bytes_by_layout[layout], k_ms_by_layout[layout]
   step_bytes = k_bytes + 4.0 * per + 4.0 * shape[1] + 4.0 * n_act * world
   achieved = k_bytes / (k_ms * 1e-3) / 1e9
   line = {
@@ -745,28 +755,31 @@ def run_sharded(args, torch, dist, device, world):
     'data': 'synthetic',
     'config': {'workload': WORKLOAD if n_neurons == N_NEURONS else f'REDUCED TWIN of C3: {n_neurons} neurons x 1000 synapses',
                'l2': 'inputs larger than L2 in total: each step streams a different part of the 8 GB matrix',
-               'sharding': f'post-synaptic neurons (matrix columns) split over {world} ranks, each shard prepared once into '
-                           'the column-blocked layout; each rank owns 1/N of the spike sources; ONE launch per step: the '
-                           'kernel pushes the compacted spikes of step s+1 into every peer over NVLink (peer stores), waits '
-                           '(bounded) for the lists of step s and scatters them; no collective on the data path'},
+               'sharding': f'post-synaptic neurons (matrix columns) split over {world} ranks; shard layout "{layout}" '
+                           f'(sharded.preferred_layout({shape[1]}): column-blocked down to 200,000 columns per rank, plain '
+                           'CSR below); each rank owns 1/N of the spike sources; ONE launch per step: the kernel pushes '
+                           'the compacted spikes of step s+1 into every peer over NVLink (peer stores), waits (bounded) '
+                           'for the lists of step s and scatters them; no collective on the data path'},
     'e2e': {'value': total_ops / (e2e['ms'] * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': e2e['h2d'],
             'd2h_bytes_per_step': e2e['d2h'], 'ms_per_step': e2e['ms'] / K,
-            'path': 'PushExchange.run_host_steps (bpl_sharded_run_host_steps: bpl_sharded_prime, then bpl_sharded_cb_step per '
-                    'step): per rank its own n/N spikes from pinned host memory in, its own slice of the result out to '
-                    'pinned host memory, every step'},
+            'path': f'PushExchange.run_host_steps (bpl_sharded_prime, then {step_call[layout]} per step, enqueued by one '
+                    'native call): per rank its own n/N spikes from pinned host memory in, its own slice of the result '
+                    'out to pinned host memory, every step'},
     'gpu_launches': K + 1,     # prime once, then one kernel per step
-    'roofline': {'bound': 'hbm', 'kernel': 'event_cb_scatter_kernel on one rank\'s prepared shard (stand-alone)',
+    'roofline': {'bound': 'hbm', 'kernel': kernel_name[layout],
                  'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': peak_src,
-                 'traffic': 1.14 * k_bytes, 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
+                 'traffic': traffic_ratio[layout] * k_bytes,
+                 'traffic_source': 'ncu dram__bytes on a reduced twin, scaled by algorithmic bytes',
                  'algorithmic_bytes_per_launch': k_bytes, 'kernel_us': k_ms * 1e3,
                  'step': {'algorithmic_bytes': step_bytes, 'us': ms / K * 1e3,
                           'frac': step_bytes / (ms / K * 1e-3) / 1e9 / peak}},
     'prepared_matrix': {'bytes': prepared.nbytes(), 'block_width': prepared.block_width, 'n_blocks': prepared.n_blocks,
                         'team_lanes': 1 << prepared.team_lanes_log2, 'prepare_ms': prepare_ms},
-    'plain_csr_shards': {'value': total_ops / (ms_csr * 1e-3), 'unit': UNIT, 'ms_per_step': ms_csr / K,
-                         'path': 'PushExchange.step (bpl_sharded_step) on the plain CSR shard, same graph-of-K-steps timing',
-                         'kernel_us': k_ms_csr * 1e3,
-                         'roofline_frac': k_bytes_csr / (k_ms_csr * 1e-3) / 1e9 / peak},
+    'other_layout': {'layout': other, 'value': total_ops / (ms_by_layout[other] * 1e-3), 'unit': UNIT,
+                     'ms_per_step': ms_by_layout[other] / K,
+                     'path': f'PushExchange step on the "{other}" shard ({step_call[other]}), same graph-of-K-steps timing',
+                     'kernel_us': k_ms_by_layout[other] * 1e3,
+                     'roofline_frac': k_bytes_by_layout[other] / (k_ms_by_layout[other] * 1e-3) / 1e9 / peak},
     'clocks': sampler.summary(),
   }
   if rank == 0:
@@ -787,7 +800,7 @@ def run_sharded(args, torch, dist, device, world):
   watchdog.cancel()
 
 
-def run_e2e_sharded(torch, dist, prepared, exchange, ev_host_mine, shape, W, K, device, want_last):
+def run_e2e_sharded(torch, dist, shard, exchange, ev_host_mine, shape, W, K, device, want_last):
   """End to end on N ranks through PushExchange.run_host_steps (bpl_sharded_run_host_steps): per step a rank copies
   ITS OWN n/N spikes of the next step from pinned host memory, runs the one-launch step (push to the peers + scatter
   of the current step) and copies ITS OWN slice of the result to pinned host memory, on three streams over rings of
@@ -799,7 +812,7 @@ def run_e2e_sharded(torch, dist, prepared, exchange, ev_host_mine, shape, W, K, 
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    ms = exchange.run_host_steps(prepared, ev_host_mine[first:first + count], y_host)
+    ms = exchange.run_host_steps(shard, ev_host_mine[first:first + count], y_host)
     torch.cuda.synchronize()
     dist.barrier()
     return ms

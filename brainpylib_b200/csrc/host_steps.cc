@@ -143,20 +143,25 @@ void bpl_run_host_steps(const char *target_name, const char *opaque, size_t opaq
     rt(cudaStreamWaitEvent(s_compute, ev.done_out[(n_groups - 1) % RING], 0));
 }
 
-// The one-launch sharded step (bpl_sharded_prime, then bpl_sharded_cb_step per step) on host-resident spike trains:
+}  // extern "C"
+
+namespace bpl {
+namespace {
+
+// The one-launch sharded step (bpl_sharded_prime, then one step launch per step) on host-resident spike trains:
 // host_events holds n_steps slices of this rank's own n_local spike sources, host_out takes this rank's n_out outputs
 // per step (slot step % out_slots).  Step i scatters the spikes of step i and pushes those of step i + 1, so the
 // spikes of steps g * group + 1 .. (g + 1) * group are the inputs of the group of steps g * group .. (g + 1) * group - 1.
 // ev_ring: 3 * group + 1 buffers of n_local events (the last one takes the spikes of step 0, which the prime call
 // pushes; the spikes of step j >= 1 go to buffer (j - 1) % (3 * group)); y_ring: 3 * group buffers of n_out floats
 // (step i scatters into buffer i % (3 * group) and zero-fills the next one).
-void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_t n_out, uint32_t block_width,
-                                int fixed_point, int scale_log2, uint32_t team_lanes_log2, int ev_is_float,
-                                uint32_t n_local, uint32_t row_offset, void *const *peer_lists, size_t slot_bytes,
-                                void *const *peer_flags, void *state, int world, int rank, int slots, uint32_t max_polls,
-                                void *const *ev_ring, void *const *y_ring, uint32_t group, const void *host_events,
-                                void *host_out, uint32_t out_slots, uint32_t n_steps, bpl_stream_t s_in,
-                                bpl_stream_t s_compute, bpl_stream_t s_out) {
+// `step(stream, y_cur, y_next, next_events)` enqueues the launch of one step on the rank's shard.
+template<typename Step>
+void sharded_run_host_steps_impl(Step step, uint32_t n_out, int ev_is_float, uint32_t n_local, uint32_t row_offset,
+                                 void *const *peer_lists, size_t slot_bytes, void *const *peer_flags, void *state,
+                                 int world, int rank, int slots, void *const *ev_ring, void *const *y_ring,
+                                 uint32_t group, const void *host_events, void *host_out, uint32_t out_slots,
+                                 uint32_t n_steps, bpl_stream_t s_in, bpl_stream_t s_compute, bpl_stream_t s_out) {
     if (group == 0 || group > MAX_GROUP) {
         set_status(BPL_ERR_ARGUMENT, "sharded host steps: group must be 1..16");
         return;
@@ -204,10 +209,8 @@ void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_
         if (g >= 2) rt(cudaStreamWaitEvent(s_compute, ev.done_out[(g - 2) % RING], 0));
         for (uint32_t i = first; i < last; ++i) {
             const bool final_step = i + 1 == n_steps;
-            bpl_sharded_cb_step(s_compute, groups, offsets, n_out, block_width, fixed_point, scale_log2, team_lanes_log2,
-                                y_ring[i % ring], final_step ? nullptr : y_ring[(i + 1) % ring],
-                                final_step ? nullptr : ev_ring[i % ring], ev_is_float, n_local, row_offset, peer_lists,
-                                slot_bytes, peer_flags, state, world, rank, slots, max_polls);
+            step(s_compute, y_ring[i % ring], final_step ? nullptr : y_ring[(i + 1) % ring],
+                 final_step ? nullptr : ev_ring[i % ring]);
         }
         rt(cudaEventRecord(ev.done_c[b], s_compute));
         rt(cudaStreamWaitEvent(s_out, ev.done_c[b], 0));
@@ -219,6 +222,46 @@ void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_
     rt(cudaEventRecord(ev.edge, s_in));
     rt(cudaStreamWaitEvent(s_compute, ev.edge, 0));
     rt(cudaStreamWaitEvent(s_compute, ev.done_out[(n_groups - 1) % RING], 0));
+}
+
+}  // namespace
+}  // namespace bpl
+
+extern "C" {
+
+// The shard in the column-blocked layout (bpl_sharded_cb_step per step).
+void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_t n_out, uint32_t block_width,
+                                int fixed_point, int scale_log2, uint32_t team_lanes_log2, int ev_is_float,
+                                uint32_t n_local, uint32_t row_offset, void *const *peer_lists, size_t slot_bytes,
+                                void *const *peer_flags, void *state, int world, int rank, int slots, uint32_t max_polls,
+                                void *const *ev_ring, void *const *y_ring, uint32_t group, const void *host_events,
+                                void *host_out, uint32_t out_slots, uint32_t n_steps, bpl_stream_t s_in,
+                                bpl_stream_t s_compute, bpl_stream_t s_out) {
+    sharded_run_host_steps_impl(
+        [&](bpl_stream_t s, void *y_cur, void *y_next, const void *next_events) {
+            bpl_sharded_cb_step(s, groups, offsets, n_out, block_width, fixed_point, scale_log2, team_lanes_log2, y_cur,
+                                y_next, next_events, ev_is_float, n_local, row_offset, peer_lists, slot_bytes, peer_flags,
+                                state, world, rank, slots, max_polls);
+        },
+        n_out, ev_is_float, n_local, row_offset, peer_lists, slot_bytes, peer_flags, state, world, rank, slots, ev_ring,
+        y_ring, group, host_events, host_out, out_slots, n_steps, s_in, s_compute, s_out);
+}
+
+// The shard as plain CSR arrays (bpl_sharded_step per step).
+void bpl_sharded_run_host_steps_csr(const void *data, const void *indices, const void *indptr, uint32_t n_row,
+                                    uint32_t n_out, int ev_is_float, uint32_t n_local, uint32_t row_offset,
+                                    void *const *peer_lists, size_t slot_bytes, void *const *peer_flags, void *state,
+                                    int world, int rank, int slots, uint32_t max_polls, void *const *ev_ring,
+                                    void *const *y_ring, uint32_t group, const void *host_events, void *host_out,
+                                    uint32_t out_slots, uint32_t n_steps, bpl_stream_t s_in, bpl_stream_t s_compute,
+                                    bpl_stream_t s_out) {
+    sharded_run_host_steps_impl(
+        [&](bpl_stream_t s, void *y_cur, void *y_next, const void *next_events) {
+            bpl_sharded_step(s, data, indices, indptr, n_row, n_out, y_cur, y_next, next_events, ev_is_float, n_local,
+                             row_offset, peer_lists, slot_bytes, peer_flags, state, world, rank, slots, max_polls);
+        },
+        n_out, ev_is_float, n_local, row_offset, peer_lists, slot_bytes, peer_flags, state, world, rank, slots, ev_ring,
+        y_ring, group, host_events, host_out, out_slots, n_steps, s_in, s_compute, s_out);
 }
 
 }  // extern "C"

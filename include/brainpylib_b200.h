@@ -373,6 +373,14 @@ void bpl_sharded_run_host_steps(const void *groups, const void *offsets, uint32_
                                 uint32_t max_polls, void *const *ev_ring, void *const *y_ring, uint32_t group,
                                 const void *host_events, void *host_out, uint32_t out_slots, uint32_t n_steps,
                                 bpl_stream_t s_in, bpl_stream_t s_compute, bpl_stream_t s_out);
+/* The same run on a shard kept as plain CSR arrays (bpl_sharded_step per step). */
+void bpl_sharded_run_host_steps_csr(const void *data, const void *indices, const void *indptr, uint32_t n_row,
+                                    uint32_t n_out, int ev_is_float, uint32_t n_local, uint32_t row_offset,
+                                    void *const *peer_lists, size_t slot_bytes, void *const *peer_flags, void *state,
+                                    int world, int rank, int slots, uint32_t max_polls, void *const *ev_ring,
+                                    void *const *y_ring, uint32_t group, const void *host_events, void *host_out,
+                                    uint32_t out_slots, uint32_t n_steps, bpl_stream_t s_in, bpl_stream_t s_compute,
+                                    bpl_stream_t s_out);
 
 /* ---- transposed event product without workspace and without allocation ------------------
  * No counterpart in the reference.  Same computation as event_csr_matvec_heter_float_float

@@ -105,9 +105,11 @@ def test_runs_shorter_than_a_group_and_ragged_last_groups(cuda, steps):
   bpl.HostSteps(prepared, shape=shape, group=3).run(ev, out)
   for s in range(steps):
     torch.testing.assert_close(out[s].to(cuda), want[s], rtol=1e-5, atol=1e-5)
-  out.fill_(float('nan'))
   ex = sharded.PushExchange(shape[0], dtype=torch.float32, device=cuda, slots=4, max_polls=100000)
-  ex.run_host_steps(prepared, ev, out, group=3)
-  ex.check()
-  for s in range(steps):
-    torch.testing.assert_close(out[s].to(cuda), want[s], rtol=1e-5, atol=1e-5)
+  for shard in (prepared, (d, ix, ptr)):              # the rank's shard in either storage
+    out.fill_(float('nan'))
+    ex.run_host_steps(shard, ev, out, group=3)
+    ex.check()
+    for s in range(steps):
+      torch.testing.assert_close(out[s].to(cuda), want[s], rtol=1e-5, atol=1e-5)
+  assert sharded.preferred_layout(500_000) == 'prepared' and sharded.preferred_layout(125_000) == 'csr'

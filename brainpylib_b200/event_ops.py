@@ -297,7 +297,7 @@ class ColumnBlockedCSR:
 
 def default_block_width(n_col, device=None, reserve=0):
   """Columns per block.  The kernel gives every column block ``P = floor(SMs / n_blocks)`` CTAs, one per SM, so the
-  choice is the number of blocks: at least ``n_col / 20480`` (a block's slice of the output and three copy buffers
+  choice is the number of blocks: at least ``n_col / 20480`` (a block's slice of the output and the copy buffers
   per warp must fit a CTA's shared memory; wide blocks mean long row segments, which stream best), and more only
   where that fills at least 10 % more of the SMs.  ``reserve``: SMs to leave free (the one-launch sharded step runs
   up to four exchanging blocks beside the scatter).  At least 1024 columns, a multiple of 32."""

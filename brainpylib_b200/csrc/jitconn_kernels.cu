@@ -479,18 +479,33 @@ jit_matmat_fill_kernel(const unsigned int seed, const double log_p, const double
     MMEntry<T> *mine = entries + static_cast<size_t>(c) * mm_list_stride(cap);
     unsigned int count = 0;
     unsigned int pos = s.ugap();
+    // The stream is a chain (state -> draw -> logarithm -> position -> loop test) and a column is one thread, so the
+    // walk is bound by latency, not by issue slots.  The draws of the next FOUR connections (weight, gap, weight, gap,
+    // ... in the stream's order) are therefore taken ahead of the loop test: only the cheap state update chains them,
+    // their logarithms and normal transforms overlap.  Draws behind the last connection of the column are thrown away;
+    // nobody else reads this column's stream.
     while (pos < k) {
-        T rand;
-        if (KIND == W_NORMAL) rand = (T) (curand_normal(&st) * w2 + w1);
-        else rand = (T) (curand_uniform(&st) * w2 + w1);
-        if (count < cap) {
-            MMEntry<T> e;
-            e.pos = pos;
-            e.w = rand;
-            mine[count] = e;
+        T w4[4];
+        unsigned int g4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (KIND == W_NORMAL) w4[u] = (T) (curand_normal(&st) * w2 + w1);
+            else w4[u] = (T) (curand_uniform(&st) * w2 + w1);
+            g4[u] = s.ugap();
         }
-        ++count;
-        pos += s.ugap();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (pos < k) {
+                if (count < cap) {
+                    MMEntry<T> e;
+                    e.pos = pos;
+                    e.w = w4[u];
+                    mine[count] = e;
+                }
+                ++count;
+                pos += g4[u];
+            }
+        }
     }
     cnt[c] = count;
     // the list ends with a position no tile contains; a list that overflowed reads as empty
